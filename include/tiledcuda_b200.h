@@ -1,0 +1,104 @@
+/* C ABI of the B200-native TiledCUDA tile-kernel path (libtiledcuda_b200.so).
+ *
+ * Every entry point takes raw device pointers, plain integer sizes and a CUDA stream, launches on
+ * that stream and returns without synchronising. Return value: 0 on success, a negative tc_status
+ * otherwise; tc_last_error() then holds a message for the calling thread. Nothing here allocates on
+ * the hot path except the one-time per-device status word, and nothing calls exit().
+ *
+ * Each declaration cites the interface of the TiledCUDA reference that it stands in for.
+ */
+#ifndef TILEDCUDA_B200_H_
+#define TILEDCUDA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* tc_stream_t; /* a cudaStream_t; NULL is the default stream */
+
+enum tc_status {
+    TC_OK = 0,
+    TC_ERR_BAD_ARG = -1,     /* null pointer, bad shape, misaligned pointer or stride */
+    TC_ERR_UNSUPPORTED = -2, /* shape or device outside what the kernels cover (needs sm_100) */
+    TC_ERR_CUDA = -3,        /* a CUDA runtime / driver call failed; message has the CUDA error */
+    TC_ERR_DEVICE = -4       /* a kernel recorded an error in the device status word */
+};
+
+/* Message of the last failing call made by this thread ("" if none). */
+const char* tc_last_error(void);
+
+/* ABI version of this library (major*1000 + minor). */
+int tc_version(void);
+
+/* Reads and clears the status word that kernels write when a bounded wait ran out or an index was
+ * out of range. Synchronises the current device. *code receives 0 when all launches were clean.
+ * Replaces the reference's CudaCheck -> exit(EXIT_FAILURE) (include/cuda_utils.hpp:20-26). */
+int tc_device_status(int* code);
+
+/* C[M,N] (fp32, row-major, leading dimension ldc) = A[M,K] (fp16, row-major, lda) * B, where B is
+ * column-major [K,N], i.e. stored as [N,K] row-major with leading dimension ldb.
+ * Needs K % 8 == 0, lda % 8 == 0, ldb % 8 == 0 and 16-byte aligned A and B.
+ * Replaces the reference's GEMM kernels `gemm` (examples/cpp/01_gemm/02_gemm_all_mem/gemm.hpp:92-155)
+ * and `simple_gemm` (examples/cpp/01_gemm/01_gemm_global_reg/gemm.hpp:59-92), and follows the C-ABI
+ * precedent `kernel_entry(__half*, __half*, float*)` (examples/python/gemm/entry.py:56-68). */
+int tc_gemm_f16_f32(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                    int64_t ldb, int64_t ldc, tc_stream_t stream);
+
+/* E[b] (fp32 [M,P]) = fp16(A[b] * B[b]) * D[b] for b in [0,batch): A fp16 [M,K] row-major; B
+ * column-major [K,N] stored as [N,K]; D column-major [N,P] stored as [P,N]. The intermediate A*B is
+ * accumulated in fp32, rounded to fp16 and never leaves the chip.
+ * Needs K % 16 == 0, K <= 128, P % 16 == 0, P <= 128, N % 8 == 0.
+ * Replaces `KeFusedGemm` (examples/cpp/02_fused_two_gemms/fused_gemm.hpp:98-181). */
+int tc_b2b_gemm_f16(const void* A, const void* B, const void* D, void* E, int64_t M, int64_t N, int64_t K,
+                    int64_t P, int64_t batch, tc_stream_t stream);
+
+/* O = softmax(scale * Q K^T) V per (batch, head), non-causal. Q [batch,heads,seq_q,head_dim],
+ * K [batch,heads,seq_kv,head_dim], O [batch,heads,seq_q,head_dim_v], all fp16 and contiguous;
+ * V is [batch,heads,seq_kv,head_dim_v] when v_is_transposed == 0, or V^T
+ * [batch,heads,head_dim_v,seq_kv] (the layout the reference's Python wrapper produces) otherwise.
+ * lse (fp32 [batch,heads,seq_q], natural log of the softmax denominator) may be NULL.
+ * Softmax statistics are fp32. Needs head_dim, head_dim_v multiples of 16 and <= 128; seq_kv % 8 == 0.
+ * Replaces `flash_attention` / `run_flash_attention` / `custom_flash_attention_op`
+ * (src/kernels/flash_attn.cu:134-312, 314-422, 424-456); the reference fixes scale = 1. */
+int tc_flash_attn_fwd_f16(const void* Q, const void* K, const void* V, void* O, float* lse, int64_t batch,
+                          int64_t heads, int64_t seq_q, int64_t seq_kv, int64_t head_dim, int64_t head_dim_v,
+                          float scale, int v_is_transposed, tc_stream_t stream);
+
+/* One LSTM cell step, gate order (i, f, g, o) as torch.nn.LSTMCell:
+ *   gates = x W^T + h_prev U^T + bias;  c_out = sigmoid(f) c_prev + sigmoid(i) tanh(g);
+ *   h_out = sigmoid(o) tanh(c_out).
+ * W fp16 [4*hidden, input], U fp16 [4*hidden, hidden], bias fp32 [4*hidden] or NULL, x fp16
+ * [batch,input], h_prev / h_out fp16 [batch,hidden], c_prev / c_out fp32 [batch,hidden].
+ * h_out must not alias h_prev; c_out may alias c_prev (updated in place). Needs input % 8 == 0, hidden % 16 == 0.
+ * The reference snapshot names this op (Makefile:3, test_lstm_cell) but ships no code for it. */
+int tc_lstm_cell_f16(const void* W, const void* U, const float* bias, const void* x, const void* h_prev,
+                     const float* c_prev, void* h_out, float* c_out, int64_t batch, int64_t input,
+                     int64_t hidden, tc_stream_t stream);
+
+/* `steps` chained LSTM cells (the recurrence of tc_lstm_cell_f16, one launch per step on `stream`):
+ * x fp16 [steps,batch,input]; h0 fp16 [batch,hidden]; c0 fp32 [batch,hidden]; h_all fp16
+ * [steps,batch,hidden] receives every h_t (its last slab is h_T); c_out fp32 [batch,hidden] receives
+ * c_T (it is also the running cell state, updated in place after the first step). c_out may alias c0.
+ * The cell state stays fp32 across steps; h_t is rounded to fp16 where it feeds the next step. */
+int tc_lstm_chain_f16(const void* W, const void* U, const float* bias, const void* x, const void* h0,
+                      const float* c0, void* h_all, float* c_out, int64_t steps, int64_t batch, int64_t input,
+                      int64_t hidden, tc_stream_t stream);
+
+/* ScatterND assignment: for each of the n index tuples t (k integers each, int64 when idx_is_int64
+ * else int32), data[idx[t,0], ..., idx[t,k-1], :] = updates[t, :], where data has `rank` dimensions
+ * `dims` (row-major, elements of elem_bytes bytes) and the slice is the product of dims[k..rank).
+ * Tuples must be unique for a deterministic result; out-of-range tuples are skipped and reported
+ * through tc_device_status(). Tables larger than 2^32 elements are fine (64-bit offsets).
+ * Replaces `scatter_nd_kernel` / `scatter_nd<T>` / `custom_scatter_op`
+ * (src/kernels/scatter_nd.cu:25-50, 52-112, 114-122) with the assignment semantics of the reference's
+ * own test oracle (tests/python/test_scatter_nd.py:46). */
+int tc_scatter_nd(void* data, const void* updates, const void* indices, int idx_is_int64, const int64_t* dims,
+                  int rank, int64_t n, int k, int elem_bytes, tc_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TILEDCUDA_B200_H_ */

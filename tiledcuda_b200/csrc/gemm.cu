@@ -1,0 +1,272 @@
+// GEMM  C[M,N] (fp32) = A[M,K] (fp16, row-major) * B (fp16, column-major [K,N] = [N,K] row-major).
+//
+// Persistent, warp-specialised sm_100a kernel, one CTA per SM:
+//   warp 0      TMA producer: 128x64 A tiles and BNx64 B tiles, 128-byte swizzle, into a ring of
+//               shared-memory stages guarded by full/empty mbarriers;
+//   warp 1      allocates TMEM and issues tcgen05.mma (M=128, N=BN, K=16; fp16 in, fp32 accumulate),
+//               tcgen05.commit releases each stage and publishes each finished accumulator;
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (one row per thread) and store fp32 rows.
+// Two accumulators live in TMEM (2 x BN columns), so the epilogue of tile i overlaps the main loop
+// of tile i+1. Tiles are walked in groups of kGroupM row-tiles so that the CTAs in flight share A and
+// B tiles through L2. Loads outside the matrices are zero-filled by TMA; stores are predicated.
+//
+// Stands in for the reference's `gemm` (examples/cpp/01_gemm/02_gemm_all_mem/gemm.hpp:92-155: cp.async
+// -> swizzled smem -> ldmatrix -> mma.sync, single stage) and cell::compute::gemm
+// (include/cell/compute/gemm.hpp:19-88).
+#include "host.h"
+#include "sm100.cuh"
+
+namespace tcb {
+
+constexpr int kGemmBM = 128;
+constexpr int kGemmBK = 64;
+constexpr int kGemmThreads = 192;
+constexpr int kGroupM = 16;
+
+template <int BN, int STAGES>
+struct GemmSmem {
+    static constexpr int kABytes = kGemmBM * kGemmBK * 2;
+    static constexpr int kBBytes = BN * kGemmBK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kBarBytes = 256;
+    static constexpr int kTotal = STAGES * kStageBytes + kBarBytes + 1024;  // + slack for 1024-B alignment
+};
+
+__device__ __forceinline__ void gemm_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+    const int per_group = kGroupM * tiles_n;
+    const int group = tile / per_group;
+    const int first_m = group * kGroupM;
+    const int rows = min(kGroupM, tiles_m - first_m);
+    const int in_group = tile - group * per_group;
+    tm = first_m + in_group % rows;
+    tn = in_group / rows;
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    float* __restrict__ C, int M, int N, int K, int64_t ldc, int tiles_m, int tiles_n,
+                    uint32_t* status) {
+    using S = GemmSmem<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = align_smem_1024(smem_raw);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * S::kABytes;
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes);
+    uint64_t* bar_empty = bar_full + STAGES;
+    uint64_t* bar_acc_full = bar_empty + STAGES;
+    uint64_t* bar_acc_empty = bar_acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_acc_empty + 2);
+    volatile uint32_t* abort_word = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_tiles = tiles_m * tiles_n;
+    const int k_blocks = (K + kGemmBK - 1) / kGemmBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&bar_acc_full[a], 1);
+            mbar_init(&bar_acc_empty[a], 4);  // one arrival per epilogue warp
+        }
+        *abort_word = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 2 * BN);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_a);
+            tma_prefetch_desc(&tmap_b);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                int tm, tn;
+                gemm_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&bar_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&bar_full[stage], S::kStageBytes);
+                    tma_load_2d(smem_a + stage * S::kABytes, &tmap_a, &bar_full[stage], kb * kGemmBK, tm * kGemmBM);
+                    tma_load_2d(smem_b + stage * S::kBBytes, &tmap_b, &bar_full[stage], kb * kGemmBK, tn * BN);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_f16_f32(kGemmBM, BN, false, false);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                if (!mbar_wait(&bar_acc_empty[acc], acc_phase ^ 1u, abort_word, kDevTimeoutMma)) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&bar_full[stage], phase, abort_word, kDevTimeoutMma)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + stage * S::kABytes), 16, 1024);
+                    const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem_b + stage * S::kBBytes), 16, 1024);
+#pragma unroll
+                    for (int k = 0; k < kGemmBK / 16; ++k) {
+                        // +32 bytes per K=16 step inside the 128-byte swizzle row (address field is in 16-B units)
+                        umma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2),
+                                    idesc, (kb | k) != 0);
+                    }
+                    umma_commit(&bar_empty[stage]);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                umma_commit(&bar_acc_full[acc]);
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue: TMEM -> registers -> global ----------------
+        const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            int tm, tn;
+            gemm_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            if (!mbar_wait_warp(&bar_acc_full[acc], acc_phase, abort_word, kDevTimeoutEpilogue)) break;
+            tc_fence_after_sync();
+            const int row = tm * kGemmBM + quarter * 32 + lane;
+            const int col0 = tn * BN;
+            float* crow = C + static_cast<int64_t>(row) * ldc;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_x32(taddr + static_cast<uint32_t>(c * 32), r);
+                tmem_ld_wait();
+                const int col = col0 + c * 32;
+                if (row < M) {
+                    if (vec_ok && col + 32 <= N) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                            __stcs(reinterpret_cast<float4*>(crow + col) + j, v);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col + j < N) crow[col + j] = __uint_as_float(r[j]);
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_acc_empty[acc]);
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 2 * BN);
+    }
+    if (threadIdx.x == 0 && *abort_word != 0) atomicMax(status, *abort_word);
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int M, int N, int K, int64_t ldc,
+                       const DeviceInfo* dev, cudaStream_t stream) {
+    using S = GemmSmem<BN, STAGES>;
+    auto kernel = gemm_f16_f32_kernel<BN, STAGES>;
+    static bool configured[64] = {};
+    if (!configured[dev->device]) {
+        TCB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+        configured[dev->device] = true;
+    }
+    const int tiles_m = (M + kGemmBM - 1) / kGemmBM;
+    const int tiles_n = (N + BN - 1) / BN;
+    const int tiles = tiles_m * tiles_n;
+    const int grid = tiles < dev->sm_count ? tiles : dev->sm_count;
+    kernel<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, C, M, N, K, ldc, tiles_m, tiles_n, dev->status_word);
+    TCB_CUDA(cudaGetLastError());
+    return TC_OK;
+}
+
+}  // namespace tcb
+
+extern "C" int tc_gemm_f16_f32(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                               int64_t ldb, int64_t ldc, tc_stream_t stream) {
+    using namespace tcb;
+    TCB_REQUIRE(A && B && C, "gemm: null pointer argument");
+    TCB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: M, N, K must be positive (got %lld, %lld, %lld)", (long long)M,
+                (long long)N, (long long)K);
+    TCB_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "gemm: a dimension does not fit in 31 bits");
+    TCB_REQUIRE(K % 8 == 0, "gemm: K = %lld is not a multiple of 8 (TMA rows are 16-byte granular)", (long long)K);
+    TCB_REQUIRE(lda >= K && ldb >= K && ldc >= N, "gemm: leading dimension smaller than the row length");
+    TCB_REQUIRE(lda % 8 == 0 && ldb % 8 == 0, "gemm: lda and ldb must be multiples of 8 elements (16 bytes)");
+    TCB_REQUIRE(aligned16(A) && aligned16(B), "gemm: A and B must be 16-byte aligned");
+    TCB_REQUIRE((reinterpret_cast<uintptr_t>(C) & 3u) == 0, "gemm: C must be 4-byte aligned");
+
+    const DeviceInfo* dev = nullptr;
+    if (int rc = current_device(&dev)) return rc;
+
+    // Narrow problems take the 128-column tile so that more CTAs are busy.
+    const int64_t tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
+    const bool use128 = (N <= 128) || (tiles256 < dev->sm_count);
+    const uint32_t bn = use128 ? 128u : 256u;
+
+    CUtensorMap ta, tb;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(lda) * 2};
+        const uint32_t box[2] = {kGemmBK, kGemmBM};
+        if (int rc = encode_tmap_f16_sw128(&ta, A, 2, dims, strides, box)) return rc;
+    }
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(ldb) * 2};
+        const uint32_t box[2] = {kGemmBK, bn};
+        if (int rc = encode_tmap_f16_sw128(&tb, B, 2, dims, strides, box)) return rc;
+    }
+    auto* st = static_cast<cudaStream_t>(stream);
+    if (use128)
+        return launch_gemm<128, 6>(ta, tb, static_cast<float*>(C), (int)M, (int)N, (int)K, ldc, dev, st);
+    return launch_gemm<256, 4>(ta, tb, static_cast<float*>(C), (int)M, (int)N, (int)K, ldc, dev, st);
+}

@@ -1,0 +1,113 @@
+// Host-side plumbing: error text, device cache, tensor-map encoding, device status word.
+#include "host.h"
+
+#include <mutex>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+namespace tcb {
+
+static thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+static constexpr int kMaxDevices = 64;
+static DeviceInfo g_dev[kMaxDevices];
+static bool g_dev_ready[kMaxDevices];
+static std::mutex g_mu;
+
+int current_device(const DeviceInfo** out) {
+    int dev = -1;
+    TCB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(TC_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (!g_dev_ready[dev]) {
+        DeviceInfo d;
+        d.device = dev;
+        TCB_CUDA(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+        TCB_CUDA(cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, dev));
+        TCB_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        TCB_CUDA(cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        if (d.cc_major != 10)
+            return fail(TC_ERR_UNSUPPORTED, "device %d is sm_%d%d; these kernels are built for sm_100a only", dev,
+                        d.cc_major, d.cc_minor);
+        TCB_CUDA(cudaMalloc(reinterpret_cast<void**>(&d.status_word), 4 * sizeof(uint32_t)));
+        TCB_CUDA(cudaMemset(d.status_word, 0, 4 * sizeof(uint32_t)));
+        g_dev[dev] = d;
+        g_dev_ready[dev] = true;
+    }
+    *out = &g_dev[dev];
+    return TC_OK;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn g_encode = nullptr;
+
+static int load_encode() {
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (g_encode) return TC_OK;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    TCB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (qres != cudaDriverEntryPointSuccess || fn == nullptr)
+        return fail(TC_ERR_CUDA, "driver has no cuTensorMapEncodeTiled (query result %d)", static_cast<int>(qres));
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    return TC_OK;
+}
+
+int encode_tmap_f16_sw128(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                          const uint64_t* strides_bytes, const uint32_t* box) {
+    if (int rc = load_encode()) return rc;
+    cuuint64_t gdim[5];
+    cuuint64_t gstride[5];
+    cuuint32_t bdim[5];
+    cuuint32_t estride[5];
+    for (int i = 0; i < rank; ++i) {
+        gdim[i] = dims[i];
+        bdim[i] = box[i];
+        estride[i] = 1;
+        if (i + 1 < rank) gstride[i] = strides_bytes[i];
+    }
+    CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, static_cast<cuuint32_t>(rank),
+                          const_cast<void*>(base), gdim, gstride, bdim, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(TC_ERR_CUDA,
+                    "cuTensorMapEncodeTiled failed with CUresult %d (rank %d, dims %llu x %llu, box %u x %u)",
+                    static_cast<int>(r), rank, (unsigned long long)dims[0], (unsigned long long)(rank > 1 ? dims[1] : 1),
+                    box[0], rank > 1 ? box[1] : 1u);
+    return TC_OK;
+}
+
+}  // namespace tcb
+
+extern "C" {
+
+const char* tc_last_error(void) { return tcb::g_err; }
+
+int tc_version(void) { return 1000; }
+
+int tc_device_status(int* code) {
+    if (code == nullptr) return tcb::fail(TC_ERR_BAD_ARG, "tc_device_status: code is NULL");
+    const tcb::DeviceInfo* dev = nullptr;
+    if (int rc = tcb::current_device(&dev)) return rc;
+    uint32_t host_word = 0;
+    TCB_CUDA(cudaDeviceSynchronize());
+    TCB_CUDA(cudaMemcpy(&host_word, dev->status_word, sizeof(host_word), cudaMemcpyDeviceToHost));
+    if (host_word != 0) TCB_CUDA(cudaMemset(dev->status_word, 0, 4 * sizeof(uint32_t)));
+    *code = static_cast<int>(host_word);
+    return TC_OK;
+}
+
+}  // extern "C"

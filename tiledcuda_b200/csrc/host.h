@@ -1,0 +1,50 @@
+// Host-side plumbing shared by the launchers: thread-local error text, CUDA call checking that
+// returns a status instead of exiting, TMA tensor-map encoding through the runtime's driver entry
+// point (so the library carries no link-time dependency on libcuda), device properties and the
+// per-device status word that kernels write on a bounded-wait timeout.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/tiledcuda_b200.h"
+
+namespace tcb {
+
+// printf-style; stores the message for tc_last_error() and returns `code`.
+int fail(int code, const char* fmt, ...);
+
+#define TCB_CUDA(expr)                                                                            \
+    do {                                                                                          \
+        cudaError_t _e = (expr);                                                                  \
+        if (_e != cudaSuccess)                                                                    \
+            return ::tcb::fail(TC_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), \
+                               __FILE__, __LINE__);                                               \
+    } while (0)
+
+#define TCB_REQUIRE(cond, ...)                                      \
+    do {                                                            \
+        if (!(cond)) return ::tcb::fail(TC_ERR_BAD_ARG, __VA_ARGS__); \
+    } while (0)
+
+struct DeviceInfo {
+    int device = -1;
+    int cc_major = 0;
+    int cc_minor = 0;
+    int sm_count = 0;
+    int max_smem_optin = 0;
+    uint32_t* status_word = nullptr;  // device memory, 4 words, zero-initialised
+};
+
+// Info for the current device (cached; thread-safe). Fails with TC_ERR_UNSUPPORTED unless sm_100.
+int current_device(const DeviceInfo** out);
+
+// Encodes a tiled fp16 tensor map with 128-byte swizzle. dims/box are innermost-first; strides_bytes has
+// rank-1 entries (stride of dims 1..rank-1). Zero fill outside the tensor.
+int encode_tmap_f16_sw128(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                          const uint64_t* strides_bytes, const uint32_t* box);
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace tcb

@@ -1,0 +1,322 @@
+// LSTM cell: gates = x W^T + h U^T + bias, then the sigmoid / tanh / state update, in one kernel.
+//
+// A CTA owns 128 batch rows and HT hidden units. Its B operand is gathered from the four gate blocks
+// of W (then U): rows [g*H + j0, g*H + j0 + HT) for g = i, f, g, o land next to each other in one
+// shared-memory tile, so a single tcgen05.mma with N = 4*HT produces all four gates of those units
+// in the same TMEM lanes (= batch rows). The K loop runs over the input features (x against W) and
+// continues over the hidden features (h against U) into the same accumulator, so the two gate GEMMs
+// are one accumulation chain. The epilogue thread of a batch row reads its i, f, g, o columns,
+// applies the nonlinearities in fp32, updates the fp32 cell state and writes h as fp16.
+//   warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..5 fused epilogue.
+//
+// The reference snapshot only names this op (Makefile:3 `test_lstm_cell`); the math is that of
+// torch.nn.LSTMCell with gate order (i, f, g, o).
+#include "host.h"
+#include "sm100.cuh"
+
+namespace tcb {
+
+constexpr int kLstmBM = 128;
+constexpr int kLstmBK = 64;
+constexpr int kLstmThreads = 192;
+
+template <int HT>
+struct LstmCfg {
+    static constexpr int kN = 4 * HT;
+    static constexpr int kABytes = kLstmBM * kLstmBK * 2;
+    static constexpr int kGateBytes = HT * kLstmBK * 2;
+    static constexpr int kBBytes = 4 * kGateBytes;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = (192 * 1024) / kStageBytes;
+    static constexpr int kSmem = kStages * kStageBytes + 256 + 1024;
+    static constexpr int kTmemCols = kN < 32 ? 32 : kN;
+};
+
+struct LstmParams {
+    const float* bias;    // [4H] or null
+    const float* c_prev;  // [B, H]
+    float* c_out;         // [B, H]
+    __half* h_out;        // [B, H]
+    int batch;
+    int input;
+    int hidden;
+    uint32_t* status;
+};
+
+__device__ __forceinline__ float sigmoid_f(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+__device__ __forceinline__ float tanh_f(float x) { return 2.f * sigmoid_f(2.f * x) - 1.f; }
+
+template <int HT>
+__global__ void __launch_bounds__(kLstmThreads, 1)
+lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                 const __grid_constant__ CUtensorMap tmap_h, const __grid_constant__ CUtensorMap tmap_u,
+                 const LstmParams p) {
+    using Cfg = LstmCfg<HT>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = align_smem_1024(smem_raw);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + Cfg::kStages * Cfg::kABytes;
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+    uint64_t* bar_empty = bar_full + Cfg::kStages;
+    uint64_t* bar_acc_full = bar_empty + Cfg::kStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_acc_full + 1);
+    volatile uint32_t* abort_word = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int j0 = blockIdx.x * HT;        // first hidden unit of this CTA
+    const int b0 = blockIdx.y * kLstmBM;   // first batch row
+    const int kb_x = (p.input + kLstmBK - 1) / kLstmBK;
+    const int kb_h = (p.hidden + kLstmBK - 1) / kLstmBK;
+    const int k_blocks = kb_x + kb_h;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::kStages; ++s) {
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_empty[s], 1);
+        }
+        mbar_init(bar_acc_full, 1);
+        *abort_word = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_x);
+            tma_prefetch_desc(&tmap_w);
+            tma_prefetch_desc(&tmap_h);
+            tma_prefetch_desc(&tmap_u);
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                if (!mbar_wait(&bar_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) break;
+                const bool from_x = kb < kb_x;
+                const CUtensorMap* ta = from_x ? &tmap_x : &tmap_h;
+                const CUtensorMap* tb = from_x ? &tmap_w : &tmap_u;
+                const int kcoord = (from_x ? kb : kb - kb_x) * kLstmBK;
+                mbar_arrive_expect_tx(&bar_full[stage], Cfg::kStageBytes);
+                tma_load_2d(smem_a + stage * Cfg::kABytes, ta, &bar_full[stage], kcoord, b0);
+#pragma unroll
+                for (int g = 0; g < 4; ++g)
+                    tma_load_2d(smem_b + stage * Cfg::kBBytes + g * Cfg::kGateBytes, tb, &bar_full[stage], kcoord,
+                                g * p.hidden + j0);
+                if (++stage == Cfg::kStages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_f16_f32(kLstmBM, Cfg::kN, false, false);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                if (!mbar_wait(&bar_full[stage], phase, abort_word, kDevTimeoutMma)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + stage * Cfg::kABytes), 16, 1024);
+                const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem_b + stage * Cfg::kBBytes), 16, 1024);
+#pragma unroll
+                for (int k = 0; k < kLstmBK / 16; ++k)
+                    umma_f16_ss(tmem_base, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2),
+                                idesc, (kb | k) != 0);
+                umma_commit(&bar_empty[stage]);
+                if (++stage == Cfg::kStages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+            if (ok) umma_commit(bar_acc_full);
+        }
+        __syncwarp();
+    } else {
+        const int quarter = warp & 3;
+        const int row = b0 + quarter * 32 + lane;
+        if (mbar_wait_warp(bar_acc_full, 0, abort_word, kDevTimeoutEpilogue)) {
+            tc_fence_after_sync();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+            for (int u0 = 0; u0 < HT; u0 += 16) {
+                uint32_t gi[16], gf[16], gg[16], go[16];
+                tmem_ld_x16(taddr + static_cast<uint32_t>(0 * HT + u0), gi);
+                tmem_ld_x16(taddr + static_cast<uint32_t>(1 * HT + u0), gf);
+                tmem_ld_x16(taddr + static_cast<uint32_t>(2 * HT + u0), gg);
+                tmem_ld_x16(taddr + static_cast<uint32_t>(3 * HT + u0), go);
+                tmem_ld_wait();
+                const int unit0 = j0 + u0;
+                if (row < p.batch && unit0 < p.hidden) {
+                    // hidden % 16 == 0, so a 16-unit group is either fully inside or fully outside
+                    const int64_t off = static_cast<int64_t>(row) * p.hidden + unit0;
+                    float c_old[16];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float4 v = *reinterpret_cast<const float4*>(p.c_prev + off + 4 * q);
+                        c_old[4 * q] = v.x;
+                        c_old[4 * q + 1] = v.y;
+                        c_old[4 * q + 2] = v.z;
+                        c_old[4 * q + 3] = v.w;
+                    }
+                    float c_new[16];
+                    uint32_t h_new[8];
+                    float hv[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        float xi = __uint_as_float(gi[i]);
+                        float xf = __uint_as_float(gf[i]);
+                        float xg = __uint_as_float(gg[i]);
+                        float xo = __uint_as_float(go[i]);
+                        if (p.bias != nullptr) {
+                            xi += __ldg(p.bias + 0 * p.hidden + unit0 + i);
+                            xf += __ldg(p.bias + 1 * p.hidden + unit0 + i);
+                            xg += __ldg(p.bias + 2 * p.hidden + unit0 + i);
+                            xo += __ldg(p.bias + 3 * p.hidden + unit0 + i);
+                        }
+                        const float c = sigmoid_f(xf) * c_old[i] + sigmoid_f(xi) * tanh_f(xg);
+                        c_new[i] = c;
+                        hv[i] = sigmoid_f(xo) * tanh_f(c);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) h_new[i] = pack_half2(hv[2 * i], hv[2 * i + 1]);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        *reinterpret_cast<float4*>(p.c_out + off + 4 * q) =
+                            make_float4(c_new[4 * q], c_new[4 * q + 1], c_new[4 * q + 2], c_new[4 * q + 3]);
+                    uint4* hd = reinterpret_cast<uint4*>(p.h_out + off);
+                    hd[0] = make_uint4(h_new[0], h_new[1], h_new[2], h_new[3]);
+                    hd[1] = make_uint4(h_new[4], h_new[5], h_new[6], h_new[7]);
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_word != 0) atomicMax(p.status, *abort_word);
+}
+
+static int encode_2d(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, uint32_t box_rows) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(rows)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(cols) * 2};
+    const uint32_t box[2] = {kLstmBK, box_rows};
+    return encode_tmap_f16_sw128(out, base, 2, dims, strides, box);
+}
+
+struct LstmWeights {
+    CUtensorMap w, u;
+    int ht;
+};
+
+static int pick_ht(const DeviceInfo* dev, int64_t batch, int64_t hidden) {
+    const int64_t ctas16 = ((hidden + 15) / 16) * ((batch + kLstmBM - 1) / kLstmBM);
+    return ctas16 <= 2 * dev->sm_count ? 16 : 32;
+}
+
+static int encode_weights(LstmWeights* lw, const DeviceInfo* dev, const void* W, const void* U, int64_t batch,
+                          int64_t input, int64_t hidden) {
+    lw->ht = pick_ht(dev, batch, hidden);
+    if (int rc = encode_2d(&lw->w, W, 4 * hidden, input, static_cast<uint32_t>(lw->ht))) return rc;
+    return encode_2d(&lw->u, U, 4 * hidden, hidden, static_cast<uint32_t>(lw->ht));
+}
+
+template <int HT>
+static int launch_lstm(const CUtensorMap& tx, const LstmWeights& lw, const CUtensorMap& th, const LstmParams& p,
+                       const DeviceInfo* dev, cudaStream_t stream) {
+    using Cfg = LstmCfg<HT>;
+    auto kernel = lstm_cell_kernel<HT>;
+    static bool configured[64] = {};
+    if (!configured[dev->device]) {
+        TCB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+        configured[dev->device] = true;
+    }
+    const dim3 grid(static_cast<unsigned>((p.hidden + HT - 1) / HT), static_cast<unsigned>((p.batch + kLstmBM - 1) / kLstmBM));
+    kernel<<<grid, kLstmThreads, Cfg::kSmem, stream>>>(tx, lw.w, th, lw.u, p);
+    TCB_CUDA(cudaGetLastError());
+    return TC_OK;
+}
+
+static int lstm_step(const LstmWeights& lw, const float* bias, const void* x, const void* h_prev, const float* c_prev,
+                     void* h_out, float* c_out, int64_t batch, int64_t input, int64_t hidden, const DeviceInfo* dev,
+                     cudaStream_t stream) {
+    CUtensorMap tx, th;
+    if (int rc = encode_2d(&tx, x, batch, input, kLstmBM)) return rc;
+    if (int rc = encode_2d(&th, h_prev, batch, hidden, kLstmBM)) return rc;
+    LstmParams p;
+    p.bias = bias;
+    p.c_prev = c_prev;
+    p.c_out = c_out;
+    p.h_out = static_cast<__half*>(h_out);
+    p.batch = static_cast<int>(batch);
+    p.input = static_cast<int>(input);
+    p.hidden = static_cast<int>(hidden);
+    p.status = dev->status_word;
+    return lw.ht == 16 ? launch_lstm<16>(tx, lw, th, p, dev, stream) : launch_lstm<32>(tx, lw, th, p, dev, stream);
+}
+
+static int check_lstm(const char* op, const void* W, const void* U, const void* x, const void* h, const float* c,
+                      void* h_out, float* c_out, int64_t batch, int64_t input, int64_t hidden) {
+    TCB_REQUIRE(W && U && x && h && c && h_out && c_out, "%s: null pointer argument", op);
+    TCB_REQUIRE(batch > 0 && input > 0 && hidden > 0, "%s: batch, input and hidden must be positive", op);
+    TCB_REQUIRE(input % 8 == 0, "%s: input = %lld must be a multiple of 8", op, (long long)input);
+    TCB_REQUIRE(hidden % 16 == 0, "%s: hidden = %lld must be a multiple of 16", op, (long long)hidden);
+    TCB_REQUIRE(4 * hidden < (1ll << 31) && batch < (1ll << 31) && input < (1ll << 31), "%s: extent too large", op);
+    TCB_REQUIRE(aligned16(W) && aligned16(U) && aligned16(x) && aligned16(h) && aligned16(c) && aligned16(h_out) &&
+                    aligned16(c_out),
+                "%s: pointers must be 16-byte aligned", op);
+    return TC_OK;
+}
+
+}  // namespace tcb
+
+extern "C" int tc_lstm_cell_f16(const void* W, const void* U, const float* bias, const void* x, const void* h_prev,
+                                const float* c_prev, void* h_out, float* c_out, int64_t batch, int64_t input,
+                                int64_t hidden, tc_stream_t stream) {
+    using namespace tcb;
+    if (int rc = check_lstm("lstm_cell", W, U, x, h_prev, c_prev, h_out, c_out, batch, input, hidden)) return rc;
+    TCB_REQUIRE(h_out != h_prev, "lstm_cell: h_out must not alias h_prev");
+    const DeviceInfo* dev = nullptr;
+    if (int rc = current_device(&dev)) return rc;
+    LstmWeights lw;
+    if (int rc = encode_weights(&lw, dev, W, U, batch, input, hidden)) return rc;
+    return lstm_step(lw, bias, x, h_prev, c_prev, h_out, c_out, batch, input, hidden, dev, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tc_lstm_chain_f16(const void* W, const void* U, const float* bias, const void* x, const void* h0,
+                                 const float* c0, void* h_all, float* c_out, int64_t steps, int64_t batch,
+                                 int64_t input, int64_t hidden, tc_stream_t stream) {
+    using namespace tcb;
+    TCB_REQUIRE(steps > 0, "lstm_chain: steps must be positive");
+    if (int rc = check_lstm("lstm_chain", W, U, x, h0, c0, h_all, c_out, batch, input, hidden)) return rc;
+    TCB_REQUIRE((batch * input) % 8 == 0 && (batch * hidden) % 8 == 0, "lstm_chain: per-step slabs must stay 16-byte aligned");
+    const DeviceInfo* dev = nullptr;
+    if (int rc = current_device(&dev)) return rc;
+    LstmWeights lw;
+    if (int rc = encode_weights(&lw, dev, W, U, batch, input, hidden)) return rc;
+    auto* st = static_cast<cudaStream_t>(stream);
+    const __half* xs = static_cast<const __half*>(x);
+    __half* hs = static_cast<__half*>(h_all);
+    for (int64_t t = 0; t < steps; ++t) {
+        const void* h_prev = t == 0 ? h0 : static_cast<const void*>(hs + (t - 1) * batch * hidden);
+        const float* c_prev = t == 0 ? c0 : c_out;
+        if (int rc = lstm_step(lw, bias, xs + t * batch * input, h_prev, c_prev, hs + t * batch * hidden, c_out, batch,
+                               input, hidden, dev, st))
+            return rc;
+    }
+    return TC_OK;
+}

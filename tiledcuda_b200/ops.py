@@ -1,0 +1,258 @@
+"""Operators of the tile-kernel path on torch CUDA tensors, each a thin call into the C ABI.
+
+Tensors supply device memory and the current stream; all arithmetic happens in the sm_100a kernels
+of libtiledcuda_b200.so. Outputs are written in place into caller-allocated tensors, as the
+reference's ops do (include/kernels/flash_attn.hpp:35-37, include/kernels/scatter_nd.hpp:39-40).
+Nothing here falls back to PyTorch: a CPU tensor, a wrong dtype or an unsupported shape raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, name: str, dtype: torch.dtype, contiguous: bool = True) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> None:
+    """c[M,N] (fp32) = a[M,K] @ b[N,K].T with fp16 inputs and fp32 accumulation.
+
+    `b` is the column-major [K,N] operand of the reference's GEMM stored as [N,K] rows, so the result
+    equals `a @ b.t()` (examples/python/gemm/main.py:21). Row strides of a, b, c may exceed the row
+    length (leading dimensions); the innermost stride must be 1.
+    """
+    for t, name, dt in ((a, "a", torch.float16), (b, "b", torch.float16), (c, "c", torch.float32)):
+        _need(t, name, dt, contiguous=False)
+        if t.dim() != 2 or t.stride(1) != 1:
+            raise ValueError(f"{name} must be 2-D with unit inner stride")
+    m, k = a.shape
+    n, kb = b.shape
+    if kb != k or tuple(c.shape) != (m, n):
+        raise ValueError(f"shape mismatch: a {tuple(a.shape)}, b {tuple(b.shape)}, c {tuple(c.shape)}")
+    lib = _lib.load()
+    with torch.cuda.device(a.device):
+        _lib.check(
+            "tc_gemm_f16_f32",
+            lib.tc_gemm_f16_f32(_ptr(a), _ptr(b), _ptr(c), m, n, k, a.stride(0), b.stride(0), c.stride(0), _stream()),
+        )
+
+
+def back2back_gemm(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, e: torch.Tensor) -> None:
+    """e (fp32 [.., M, P]) = fp16(a @ b.T) @ d.T, the intermediate kept on chip.
+
+    a fp16 [batch, M, K] or [M, K]; b fp16 [.., N, K] (column-major [K,N]); d fp16 [.., P, N]
+    (column-major [N,P]); as in KeFusedGemm (examples/cpp/02_fused_two_gemms/fused_gemm.hpp:98-181).
+    """
+    for t, name, dt in ((a, "a", torch.float16), (b, "b", torch.float16), (d, "d", torch.float16), (e, "e", torch.float32)):
+        _need(t, name, dt)
+    if a.dim() not in (2, 3) or b.dim() != a.dim() or d.dim() != a.dim() or e.dim() != a.dim():
+        raise ValueError("a, b, d, e must all be 2-D or all be 3-D (batched)")
+    batch = a.shape[0] if a.dim() == 3 else 1
+    m, k = a.shape[-2:]
+    n, kb = b.shape[-2:]
+    p, nd = d.shape[-2:]
+    if kb != k or nd != n or tuple(e.shape[-2:]) != (m, p):
+        raise ValueError(f"shape mismatch: a {tuple(a.shape)}, b {tuple(b.shape)}, d {tuple(d.shape)}, e {tuple(e.shape)}")
+    if a.dim() == 3 and not (b.shape[0] == d.shape[0] == e.shape[0] == batch):
+        raise ValueError("batch sizes differ")
+    lib = _lib.load()
+    with torch.cuda.device(a.device):
+        _lib.check("tc_b2b_gemm_f16", lib.tc_b2b_gemm_f16(_ptr(a), _ptr(b), _ptr(d), _ptr(e), m, n, k, p, batch, _stream()))
+
+
+def flash_attn(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    o: torch.Tensor,
+    scale: float | None = None,
+    lse: torch.Tensor | None = None,
+    v_is_transposed: bool = False,
+) -> None:
+    """o = softmax(scale * q k^T) v per (batch, head); non-causal; fp32 statistics.
+
+    q [B,H,Sq,D], k [B,H,Skv,D], o [B,H,Sq,Dv] fp16; v [B,H,Skv,Dv], or [B,H,Dv,Skv] when
+    v_is_transposed. scale defaults to 1/sqrt(D). lse, if given, is fp32 [B,H,Sq].
+    """
+    for t, name in ((q, "q"), (k, "k"), (v, "v"), (o, "o")):
+        _need(t, name, torch.float16)
+        if t.dim() != 4:
+            raise ValueError(f"{name} must be 4-D [batch, heads, seq, dim]")
+    b, h, sq, d = q.shape
+    skv = k.shape[2]
+    dv = v.shape[2] if v_is_transposed else v.shape[3]
+    v_expect = (b, h, dv, skv) if v_is_transposed else (b, h, skv, dv)
+    if tuple(k.shape) != (b, h, skv, d) or tuple(v.shape) != v_expect or tuple(o.shape) != (b, h, sq, dv):
+        raise ValueError(f"shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}, o {tuple(o.shape)}")
+    if lse is not None:
+        _need(lse, "lse", torch.float32)
+        if tuple(lse.shape) != (b, h, sq):
+            raise ValueError("lse must be [batch, heads, seq_q]")
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    lib = _lib.load()
+    with torch.cuda.device(q.device):
+        _lib.check(
+            "tc_flash_attn_fwd_f16",
+            lib.tc_flash_attn_fwd_f16(
+                _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), b, h, sq, skv, d, dv, float(scale),
+                int(bool(v_is_transposed)), _stream(),
+            ),
+        )
+
+
+def flash_attention_fwd(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, O: torch.Tensor, m: int, n: int, k: int, p: int) -> None:
+    """The reference's op, argument for argument (src/kernels/flash_attn.cu:424-456).
+
+    Flattened fp16 buffers: Q is [m,k] row-major, K is [n,k] row-major (K as [seq, dim]), V is V^T
+    = [p,n] row-major, O is [m,p]; one head, no softmax scale. Any m, n and k, p <= 128 that the
+    kernel covers are accepted, not only the reference's three hard-coded shapes.
+    """
+    for t, name, numel in ((Q, "Q", m * k), (K, "K", n * k), (V, "V", n * p), (O, "O", m * p)):
+        _need(t, name, torch.float16)
+        if t.numel() != numel:
+            raise ValueError(f"{name} has {t.numel()} elements, expected {numel}")
+    lib = _lib.load()
+    with torch.cuda.device(Q.device):
+        _lib.check(
+            "tc_flash_attn_fwd_f16",
+            lib.tc_flash_attn_fwd_f16(_ptr(Q), _ptr(K), _ptr(V), _ptr(O), _ptr(None), 1, 1, m, n, k, p, 1.0, 1, _stream()),
+        )
+
+
+def lstm_cell(
+    w: torch.Tensor,
+    u: torch.Tensor,
+    bias: torch.Tensor | None,
+    x: torch.Tensor,
+    h_prev: torch.Tensor,
+    c_prev: torch.Tensor,
+    h_out: torch.Tensor,
+    c_out: torch.Tensor,
+) -> None:
+    """One LSTM cell step with gate order (i, f, g, o) as torch.nn.LSTMCell.
+
+    gates = x @ w.T + h_prev @ u.T + bias; c_out = sigmoid(f) * c_prev + sigmoid(i) * tanh(g);
+    h_out = sigmoid(o) * tanh(c_out). w fp16 [4H, I]; u fp16 [4H, H]; bias fp32 [4H] or None; x fp16
+    [B, I]; h fp16 [B, H]; c fp32 [B, H].
+    """
+    _need(w, "w", torch.float16)
+    _need(u, "u", torch.float16)
+    _need(x, "x", torch.float16)
+    _need(h_prev, "h_prev", torch.float16)
+    _need(h_out, "h_out", torch.float16)
+    _need(c_prev, "c_prev", torch.float32)
+    _need(c_out, "c_out", torch.float32)
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    batch, inp = x.shape
+    hidden = u.shape[1]
+    if tuple(w.shape) != (4 * hidden, inp) or tuple(u.shape) != (4 * hidden, hidden):
+        raise ValueError(f"weight shapes {tuple(w.shape)}, {tuple(u.shape)} do not match input {inp}, hidden {hidden}")
+    for t, name in ((h_prev, "h_prev"), (h_out, "h_out"), (c_prev, "c_prev"), (c_out, "c_out")):
+        if tuple(t.shape) != (batch, hidden):
+            raise ValueError(f"{name} must be [{batch}, {hidden}]")
+    if bias is not None and bias.numel() != 4 * hidden:
+        raise ValueError("bias must have 4*hidden elements")
+    if h_out.data_ptr() == h_prev.data_ptr():
+        raise ValueError("h_out must not alias h_prev")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        _lib.check(
+            "tc_lstm_cell_f16",
+            lib.tc_lstm_cell_f16(_ptr(w), _ptr(u), _ptr(bias), _ptr(x), _ptr(h_prev), _ptr(c_prev), _ptr(h_out),
+                                 _ptr(c_out), batch, inp, hidden, _stream()),
+        )
+
+
+def lstm_chain(
+    w: torch.Tensor,
+    u: torch.Tensor,
+    bias: torch.Tensor | None,
+    x: torch.Tensor,
+    h0: torch.Tensor,
+    c0: torch.Tensor,
+    h_all: torch.Tensor,
+    c_out: torch.Tensor,
+) -> None:
+    """`steps` chained cells: x fp16 [T, B, I]; h_all fp16 [T, B, H] gets every h_t; c_out fp32 [B, H] gets c_T."""
+    _need(w, "w", torch.float16)
+    _need(u, "u", torch.float16)
+    _need(x, "x", torch.float16)
+    _need(h0, "h0", torch.float16)
+    _need(h_all, "h_all", torch.float16)
+    _need(c0, "c0", torch.float32)
+    _need(c_out, "c_out", torch.float32)
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    steps, batch, inp = x.shape
+    hidden = u.shape[1]
+    if tuple(w.shape) != (4 * hidden, inp) or tuple(u.shape) != (4 * hidden, hidden):
+        raise ValueError("weight shapes do not match x / hidden size")
+    if tuple(h_all.shape) != (steps, batch, hidden) or tuple(h0.shape) != (batch, hidden):
+        raise ValueError("h_all must be [steps, batch, hidden] and h0 [batch, hidden]")
+    if tuple(c0.shape) != (batch, hidden) or tuple(c_out.shape) != (batch, hidden):
+        raise ValueError("c0 and c_out must be [batch, hidden]")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        _lib.check(
+            "tc_lstm_chain_f16",
+            lib.tc_lstm_chain_f16(_ptr(w), _ptr(u), _ptr(bias), _ptr(x), _ptr(h0), _ptr(c0), _ptr(h_all), _ptr(c_out),
+                                  steps, batch, inp, hidden, _stream()),
+        )
+
+
+def scatter_nd(data: torch.Tensor, indices: torch.Tensor, updates: torch.Tensor) -> None:
+    """data[indices[t, 0], ..., indices[t, k-1]] = updates[t] for every index tuple t (in place).
+
+    data is N-D and contiguous; indices is int32 or int64 [..., k]; updates holds one slice
+    data.shape[k:] per tuple. Tuples must be unique for a deterministic result. Argument order follows
+    the reference's Python wrapper (pytiledcuda/__init__.py:6-8): data, indices, updates.
+    """
+    if not data.is_cuda or not indices.is_cuda or not updates.is_cuda:
+        raise ValueError("scatter_nd needs CUDA tensors (there is no CPU path)")
+    if indices.dtype not in (torch.int32, torch.int64):
+        raise TypeError(f"indices must be int32 or int64, got {indices.dtype}")
+    if updates.dtype != data.dtype:
+        raise TypeError("updates and data must have the same dtype")
+    if not (data.is_contiguous() and indices.is_contiguous() and updates.is_contiguous()):
+        raise ValueError("data, indices and updates must be contiguous")
+    if indices.dim() < 1:
+        raise ValueError("indices must have at least one dimension")
+    k = indices.shape[-1]
+    n = indices.numel() // k if k else 0
+    if k < 1 or k > data.dim():
+        raise ValueError(f"index tuple length {k} does not fit data of rank {data.dim()}")
+    slice_elems = 1
+    for s in data.shape[k:]:
+        slice_elems *= s
+    if updates.numel() != n * slice_elems:
+        raise ValueError(f"updates has {updates.numel()} elements, expected {n} slices of {slice_elems}")
+    dims = (ctypes.c_int64 * data.dim())(*data.shape)
+    lib = _lib.load()
+    with torch.cuda.device(data.device):
+        _lib.check(
+            "tc_scatter_nd",
+            lib.tc_scatter_nd(_ptr(data), _ptr(updates), _ptr(indices), int(indices.dtype == torch.int64), dims,
+                              data.dim(), n, k, data.element_size(), _stream()),
+        )
