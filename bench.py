@@ -1,0 +1,602 @@
+#!/usr/bin/env python
+"""Benchmark of the tile-kernel path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+Prints ONE JSON line (rank 0). The headline workload is the fp16 GEMM 8192^3 (fp32 accumulate and
+output), the configuration the TFLOP/s metric and its target are quoted on; a "step" is one GEMM.
+With N > 1 (launched under torchrun, one rank per GPU) every rank computes its own 8192-row slab
+of a GEMM with M = 8192*N against the replicated B: weak scaling, no collective on the data path;
+the optional all-gather that assembles C on every rank is timed separately and reported under
+"assemble". `value` counts the work of all ranks over the max-over-ranks device time.
+
+Other workloads of the path (B2B GEMM, attention forward, LSTM chain, scatter_nd, GEMM sizes) are
+timed briefly at N = 1 and reported under "others"; `--workload` makes any of them the headline.
+`--impl reference` times the reference's CPU path for the same workload (the torch fp32 computation
+its own tests use as ground truth) on the host cores, on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+NOMINAL_TFLOPS = 2250.0
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_TFLOPS = 1590.0
+FALLBACK_HBM_GBS = 6650.0
+SEED = 1234  # the seed of the reference's Python tests
+
+# DRAM bytes (read + write) per launch of the dominant kernel, from the ncu captures summarised under
+# profiles/ (file named per entry). None where no capture exists.
+NCU_TRAFFIC_BYTES: dict[str, int | None] = {
+    "gemm8192": None,
+    "scatter": None,
+}
+
+
+def measured_peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"tflops": float(d["bf16_tflops"]), "tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"tflops": FALLBACK_TFLOPS, "tflops_sustained": 1400.0, "hbm_gbs": FALLBACK_HBM_GBS, "source": "fallback"}
+
+
+# ----------------------------------------------------------------------------------------------------
+# clocks
+# ----------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while a timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------------------------------------------
+# workloads: each returns the tensors it needs and a step() that launches on the current stream
+# ----------------------------------------------------------------------------------------------------
+class Workload:
+    name = ""
+    metric = ""
+    unit = "TFLOP/s"
+    dtype = "f16"
+    bound = "tensor"
+
+    def units_per_step(self) -> float:  # FLOP (or bytes) per step on one rank
+        raise NotImplementedError
+
+    def setup(self, device, rank: int):
+        raise NotImplementedError
+
+    def step(self):
+        raise NotImplementedError
+
+    def launches_per_step(self) -> int:
+        return 1
+
+    def describe(self) -> dict:
+        return {}
+
+    # end-to-end leg: host buffers, copies inside the timed region
+    def e2e_setup(self):
+        raise NotImplementedError
+
+    def e2e_step(self):
+        raise NotImplementedError
+
+    def e2e_bytes(self) -> tuple[int, int]:
+        raise NotImplementedError
+
+    # CPU leg (the reference's torch fp32 computation), bounded sample
+    def cpu_sample(self):
+        """Returns (callable, units_done_per_call, description)."""
+        raise NotImplementedError
+
+
+class GemmWorkload(Workload):
+    def __init__(self, n: int):
+        self.n = n
+        self.name = f"gemm{n}"
+        self.metric = f"fp16 GEMM {n}^3 TFLOP/s (fp32 accumulate, fp32 output)"
+
+    def units_per_step(self):
+        return 2.0 * self.n ** 3
+
+    def setup(self, device, rank):
+        n = self.n
+        g = torch.Generator(device=device).manual_seed(SEED + rank)
+        self.a = (torch.rand(n, n, generator=g, device=device) * 2 - 1).half()
+        gb = torch.Generator(device=device).manual_seed(SEED)
+        self.b = (torch.rand(n, n, generator=gb, device=device) * 2 - 1).half()
+        self.c = torch.empty(n, n, device=device)
+
+    def step(self):
+        from tiledcuda_b200 import ops
+        ops.gemm(self.a, self.b, self.c)
+
+    def describe(self):
+        n = self.n
+        footprint = 2 * n * n * 2 + n * n * 4
+        return {"M_per_gpu": n, "N": n, "K": n, "a": "row-major fp16", "b": "col-major fp16 ([N,K] rows)", "c": "fp32",
+                "l2": "inputs+output larger than L2" if footprint > 126e6 else "L2 flushed between steps",
+                "flush_l2": footprint <= 126e6}
+
+    def e2e_setup(self):
+        self.ha = self.a.cpu().pin_memory()
+        self.hb = self.b.cpu().pin_memory()
+        self.hc = torch.empty(self.n, self.n, dtype=torch.float32).pin_memory()
+
+    def e2e_step(self):
+        from tiledcuda_b200 import ops
+        self.a.copy_(self.ha, non_blocking=True)
+        self.b.copy_(self.hb, non_blocking=True)
+        ops.gemm(self.a, self.b, self.c)
+        self.hc.copy_(self.c, non_blocking=True)
+
+    def e2e_bytes(self):
+        return 2 * self.n * self.n * 2, self.n * self.n * 4
+
+    def cpu_sample(self):
+        n = self.n
+        rows = min(n, max(128, int(2.0e11 / (2.0 * n * n)) // 128 * 128))
+        a = self.a[:rows].cpu() if hasattr(self, "a") else (torch.rand(rows, n) * 2 - 1).half()
+        b = self.b.cpu() if hasattr(self, "b") else (torch.rand(n, n) * 2 - 1).half()
+        a32, b32 = a.float(), b.float()
+
+        def run():
+            return a32 @ b32.t()
+
+        return run, 2.0 * rows * n * n, f"{rows} of {n} rows of A against the full B (fp32 torch matmul), scaled by FLOPs"
+
+
+class B2bWorkload(Workload):
+    name = "b2b"
+    metric = "fp16 back-to-back GEMM 16384x128x128x128 TFLOP/s"
+    bound = "hbm"
+
+    def units_per_step(self):
+        return 2.0 * 16384 * 128 * 128 * 2
+
+    def bytes_per_step(self):
+        return 2 * (16384 * 128 + 128 * 128 + 128 * 128) + 4 * 16384 * 128
+
+    def setup(self, device, rank):
+        g = torch.Generator(device=device).manual_seed(SEED + rank)
+        self.a = (torch.randn(16384, 128, generator=g, device=device) * 0.1).half()
+        self.b = (torch.randn(128, 128, generator=g, device=device) * 0.1).half()
+        self.d = (torch.randn(128, 128, generator=g, device=device) * 0.1).half()
+        self.e = torch.empty(16384, 128, device=device)
+
+    def step(self):
+        from tiledcuda_b200 import ops
+        ops.back2back_gemm(self.a, self.b, self.d, self.e)
+
+    def cpu_sample(self):
+        a, b, d = self.a.cpu().float(), self.b.cpu().float(), self.d.cpu().float()
+
+        def run():
+            return ((a @ b.t()).half().float()) @ d.t()
+
+        return run, self.units_per_step(), "full problem (fp32 torch, intermediate rounded to fp16)"
+
+
+class AttentionWorkload(Workload):
+    name = "fa"
+    metric = "FlashAttention-2 forward b16 h32 s4096 d128 TFLOP/s"
+
+    def __init__(self, batch=16, heads=32, seq=4096, dim=128):
+        self.batch, self.heads, self.seq, self.dim = batch, heads, seq, dim
+
+    def units_per_step(self):
+        return 4.0 * self.batch * self.heads * self.seq * self.seq * self.dim
+
+    def setup(self, device, rank):
+        g = torch.Generator(device=device).manual_seed(SEED + rank)
+        shape = (self.batch, self.heads, self.seq, self.dim)
+        self.q = torch.randn(shape, generator=g, device=device, dtype=torch.float16)
+        self.k = torch.randn(shape, generator=g, device=device, dtype=torch.float16)
+        self.v = torch.randn(shape, generator=g, device=device, dtype=torch.float16)
+        self.o = torch.empty_like(self.q)
+
+    def step(self):
+        from tiledcuda_b200 import ops
+        ops.flash_attn(self.q, self.k, self.v, self.o)
+
+    def cpu_sample(self):
+        heads = 4
+        q, k, v = (t[0, :heads].cpu().float() for t in (self.q, self.k, self.v))
+        scale = 1.0 / math.sqrt(self.dim)
+
+        def run():
+            return torch.softmax((q @ k.transpose(-1, -2)) * scale, dim=-1) @ v
+
+        return run, 4.0 * heads * self.seq * self.seq * self.dim, f"1 batch x {heads} heads of {self.batch}x{self.heads} (fp32 torch), scaled by FLOPs"
+
+
+class LstmWorkload(Workload):
+    name = "lstm"
+    metric = "LSTM chain b256 i1024 h1024 x64 steps TFLOP/s"
+    steps, batch, inp, hidden = 64, 256, 1024, 1024
+
+    def units_per_step(self):
+        return 2.0 * 4 * self.hidden * (self.inp + self.hidden) * self.batch * self.steps
+
+    def setup(self, device, rank):
+        g = torch.Generator(device=device).manual_seed(SEED + rank)
+        self.w = (torch.randn(4 * self.hidden, self.inp, generator=g, device=device) * 0.02).half()
+        self.u = (torch.randn(4 * self.hidden, self.hidden, generator=g, device=device) * 0.02).half()
+        self.x = torch.randn(self.steps, self.batch, self.inp, generator=g, device=device).half()
+        self.h0 = torch.zeros(self.batch, self.hidden, dtype=torch.float16, device=device)
+        self.c0 = torch.zeros(self.batch, self.hidden, device=device)
+        self.h_all = torch.empty(self.steps, self.batch, self.hidden, dtype=torch.float16, device=device)
+        self.c_t = torch.empty(self.batch, self.hidden, device=device)
+
+    def step(self):
+        from tiledcuda_b200 import ops
+        ops.lstm_chain(self.w, self.u, None, self.x, self.h0, self.c0, self.h_all, self.c_t)
+
+    def launches_per_step(self):
+        return self.steps
+
+    def cpu_sample(self):
+        from oracle import oracle
+        w, u, x, h0, c0 = (t.cpu() for t in (self.w, self.u, self.x, self.h0, self.c0))
+
+        def run():
+            return oracle.lstm_chain(w, u, None, x, h0, c0)
+
+        return run, self.units_per_step(), "full 64-step chain (fp32 torch)"
+
+
+class ScatterWorkload(Workload):
+    name = "scatter"
+    metric = "scatter_nd 2^24 rows into [2^26, 8] fp16 GB/s"
+    unit = "GB/s"
+    dtype = "i32 index / 16-byte rows"
+    bound = "hbm"
+    rows, width, n = 1 << 26, 8, 1 << 24
+    rotate = 4  # update / index sets rotated so that no step finds its inputs in L2
+
+    def units_per_step(self):
+        return float(self.n * (4 + 16 + 16))
+
+    def setup(self, device, rank):
+        g = torch.Generator(device=device).manual_seed(SEED + rank)
+        self.table = torch.randn(self.rows, self.width, generator=g, device=device, dtype=torch.float16)
+        self.idx = [torch.randperm(self.rows, generator=g, device=device)[: self.n].to(torch.int32).view(-1, 1).contiguous()
+                    for _ in range(self.rotate)]
+        self.upd = [torch.randn(self.n, self.width, generator=g, device=device, dtype=torch.float16) for _ in range(self.rotate)]
+        self.i = 0
+
+    def step(self):
+        from tiledcuda_b200 import ops
+        j = self.i % self.rotate
+        self.i += 1
+        ops.scatter_nd(self.table, self.idx[j], self.upd[j])
+
+    def describe(self):
+        return {"table": "[2^26, 8] fp16", "updates": "2^24 unique rows", "l2": f"{self.rotate} rotating index/update sets (320 MB each) larger than L2"}
+
+    def cpu_sample(self):
+        table = self.table.cpu()
+        idx = self.idx[0].cpu().view(-1).long()
+        upd = self.upd[0].cpu()
+
+        def run():
+            table[idx] = upd
+            return table
+
+        return run, self.units_per_step(), "full problem (torch index assignment)"
+
+
+def make_workload(name: str) -> Workload:
+    if name.startswith("gemm"):
+        return GemmWorkload(int(name[4:]))
+    return {"b2b": B2bWorkload, "fa": AttentionWorkload, "lstm": LstmWorkload, "scatter": ScatterWorkload}[name]()
+
+
+# ----------------------------------------------------------------------------------------------------
+# timing
+# ----------------------------------------------------------------------------------------------------
+def flush_l2(device, scratch=[None]):
+    if scratch[0] is None:
+        scratch[0] = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    scratch[0].fill_(1)
+
+
+def time_steps(fn, steps: int, warmup: int, barrier, flush=False, device=None) -> float:
+    """Milliseconds per step on the device, CUDA events on the launching stream, barrier + sync on both sides."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    barrier()
+    if flush:
+        total = 0.0
+        for _ in range(steps):
+            flush_l2(device)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            total += e0.elapsed_time(e1)
+        barrier()
+        return total / steps
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    return e0.elapsed_time(e1) / steps
+
+
+def roofline(w: Workload, ms: float, peaks: dict) -> dict:
+    if w.bound == "tensor":
+        achieved = w.units_per_step() / w.launches_per_step() / (ms / w.launches_per_step() * 1e-3) / 1e12
+        peak, unit, nominal = peaks["tflops"], "TFLOP/s", NOMINAL_TFLOPS
+    else:
+        nbytes = w.bytes_per_step() if hasattr(w, "bytes_per_step") else w.units_per_step()
+        achieved = nbytes / (ms * 1e-3) / 1e9
+        peak, unit, nominal = peaks["hbm_gbs"], "GB/s", NOMINAL_HBM_GBS
+    return {"bound": w.bound, "achieved": round(achieved, 2), "peak": peak, "unit": unit, "frac": round(achieved / peak, 4),
+            "peak_source": peaks["source"], "frac_of_nominal": round(achieved / nominal, 4), "traffic": NCU_TRAFFIC_BYTES.get(w.name)}
+
+
+def cpu_baseline(w: Workload, reps: int = 2) -> dict:
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    run, units, sample = w.cpu_sample()
+    run()
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        run()
+        best = min(best, time.perf_counter() - t0)
+    scale = 1e12 if w.unit == "TFLOP/s" else 1e9
+    return {"value": round(units / best / scale, 4), "unit": w.unit, "cores": threads, "kind": "port",
+            "sample": sample, "seconds_per_sample": round(best, 4)}
+
+
+def run_reference_arm(args, w: Workload, rank: int) -> int:
+    """The reference's CPU path (its tests' torch fp32 computation) on the host cores; rank 0 only."""
+    if rank != 0:
+        return 0
+    # inputs on the host: build the workload's CPU sample without touching a GPU
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    run, units, sample = _cpu_only_sample(w)
+    for _ in range(max(1, min(args.warmup, 2))):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        run()
+    dt = (time.perf_counter() - t0) / args.steps
+    scale = 1e12 if w.unit == "TFLOP/s" else 1e9
+    value = round(units / dt / scale, 4)
+    line = {
+        "impl": "reference", "metric": w.metric, "value": value, "unit": w.unit, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 (torch CPU reference of the fp16 op)", "data": "synthetic",
+        "config": {"workload": w.name, **w.describe()},
+        "cpu_baseline": {"value": value, "unit": w.unit, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": w.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def _cpu_only_sample(w: Workload):
+    """CPU sample with inputs generated on the host (no GPU involved)."""
+    if isinstance(w, GemmWorkload):
+        n = w.n
+        rows = min(n, max(128, int(2.0e11 / (2.0 * n * n)) // 128 * 128))
+        g = torch.Generator().manual_seed(SEED)
+        a32 = (torch.rand(rows, n, generator=g) * 2 - 1).half().float()
+        b32 = (torch.rand(n, n, generator=g) * 2 - 1).half().float()
+        return (lambda: a32 @ b32.t()), 2.0 * rows * n * n, f"{rows} of {n} rows of A against the full B (fp32 torch matmul), scaled by FLOPs"
+    w.setup(torch.device("cpu"), 0)
+    return w.cpu_sample()
+
+
+# ----------------------------------------------------------------------------------------------------
+# main
+# ----------------------------------------------------------------------------------------------------
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="gemm8192",
+                    help="gemm<N> | b2b | fa | lstm | scatter (default gemm8192)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-others", action="store_true", help="skip the brief timing of the other workloads")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    w = make_workload(args.workload)
+
+    if args.impl == "reference":
+        return run_reference_arm(args, w, rank)
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernels are sm_100a only and there is no CPU path")
+    from tiledcuda_b200 import _lib
+    _lib.load()  # fail loudly if the native library is missing
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    distributed = world > 1
+    if distributed:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+        barrier = lambda: (dist.barrier(), torch.cuda.synchronize())
+    else:
+        barrier = lambda: torch.cuda.synchronize()
+
+    peaks = measured_peaks()
+    w.setup(device, rank)
+    desc = w.describe()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms = time_steps(w.step, args.steps, args.warmup, barrier, flush=bool(desc.get("flush_l2")), device=device)
+    clocks = sampler.stop()
+    status = _lib.device_status()
+
+    ms_t = torch.tensor([ms], device=device, dtype=torch.float64)
+    if distributed:
+        dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
+    ms_max = ms_t.item()
+    scale = 1e12 if w.unit == "TFLOP/s" else 1e9
+    value = w.units_per_step() * world / (ms_max * 1e-3) / scale
+
+    # assemble leg (multi-GPU): all-gather of the output slabs, timed on its own
+    assemble = None
+    if distributed and isinstance(w, GemmWorkload):
+        full = torch.empty(world * w.n, w.n, device=device)
+        full[rank * w.n:(rank + 1) * w.n].copy_(w.c)
+
+        def gather():
+            dist.all_gather_into_tensor(full, full[rank * w.n:(rank + 1) * w.n])
+
+        g_ms = time_steps(gather, max(3, args.steps // 4), 2, barrier)
+        g_t = torch.tensor([g_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(g_t, op=dist.ReduceOp.MAX)
+        assemble = {"collective": "nccl all_gather of C (fp32)", "ms": round(g_t.item(), 4),
+                    "bytes_received_per_gpu": (world - 1) * w.n * w.n * 4,
+                    "bus_gbs": round((world - 1) * w.n * w.n * 4 / (g_t.item() * 1e-3) / 1e9, 1)}
+        del full
+
+    # end-to-end leg: host buffers, copies inside the timed region
+    e2e = None
+    if isinstance(w, GemmWorkload) and not args.no_e2e:
+        w.e2e_setup()
+        e_steps = max(3, min(args.steps, 10))
+        e_ms = time_steps(w.e2e_step, e_steps, 3, barrier)
+        e_t = torch.tensor([e_ms], device=device, dtype=torch.float64)
+        if distributed:
+            dist.all_reduce(e_t, op=dist.ReduceOp.MAX)
+        h2d, d2h = w.e2e_bytes()
+        e2e = {"value": round(w.units_per_step() * world / (e_t.item() * 1e-3) / scale, 3), "unit": w.unit,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(e_t.item(), 3), "steps": e_steps}
+
+    line = {
+        "metric": w.metric, "value": round(value, 2), "unit": w.unit, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms_max, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+        "config": {"workload": w.name, **desc, "parallelism": f"dp{world} (row slabs, no data-path collective)"},
+        "roofline": roofline(w, ms, peaks),
+        "clocks": clocks,
+        "gpu_launches": args.steps * w.launches_per_step(),
+        "device_status": status,
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    if assemble is not None:
+        line["assemble"] = assemble
+
+    if rank == 0 and world == 1:
+        if not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(w)
+        if not args.no_others:
+            others = {}
+            del w
+            torch.cuda.empty_cache()
+            for name in ("gemm1024", "gemm2048", "gemm4096", "gemm16384", "b2b", "fa", "lstm", "scatter"):
+                if name == args.workload:
+                    continue
+                ow = make_workload(name)
+                ow.setup(device, 0)
+                od = ow.describe()
+                steps = 10 if name != "gemm16384" else 5
+                oms = time_steps(ow.step, steps, 3, barrier, flush=bool(od.get("flush_l2")), device=device)
+                oscale = 1e12 if ow.unit == "TFLOP/s" else 1e9
+                others[name] = {"metric": ow.metric, "value": round(ow.units_per_step() / (oms * 1e-3) / oscale, 2), "unit": ow.unit,
+                                "ms_per_step": round(oms, 4), "roofline": roofline(ow, oms, peaks), "launches_per_step": ow.launches_per_step()}
+                del ow
+                torch.cuda.empty_cache()
+            others["device_status"] = _lib.device_status()
+            line["others"] = others
+
+    if distributed:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

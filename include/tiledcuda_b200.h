@@ -82,7 +82,8 @@ int tc_lstm_cell_f16(const void* W, const void* U, const float* bias, const void
  * x fp16 [steps,batch,input]; h0 fp16 [batch,hidden]; c0 fp32 [batch,hidden]; h_all fp16
  * [steps,batch,hidden] receives every h_t (its last slab is h_T); c_out fp32 [batch,hidden] receives
  * c_T (it is also the running cell state, updated in place after the first step). c_out may alias c0.
- * The cell state stays fp32 across steps; h_t is rounded to fp16 where it feeds the next step. */
+ * The cell state stays fp32 across steps; h_t is rounded to fp16 where it feeds the next step.
+ * Like the cell, it has no code in the reference snapshot (Makefile:3 only names test_lstm_cell). */
 int tc_lstm_chain_f16(const void* W, const void* U, const float* bias, const void* x, const void* h0,
                       const float* c0, void* h_all, float* c_out, int64_t steps, int64_t batch, int64_t input,
                       int64_t hidden, tc_stream_t stream);

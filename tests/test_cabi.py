@@ -1,0 +1,88 @@
+"""CPU tests of the C-ABI boundary: the library loads without a GPU, exports every symbol that
+include/tiledcuda_b200.h declares, and rejects bad arguments with a status and a message before it
+touches CUDA. No compute call is made here."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from tiledcuda_b200 import _lib
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "tiledcuda_b200.h"
+
+
+def declared_symbols():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(tc_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_symbols()
+    for want in ("tc_gemm_f16_f32", "tc_b2b_gemm_f16", "tc_flash_attn_fwd_f16", "tc_lstm_cell_f16",
+                 "tc_lstm_chain_f16", "tc_scatter_nd", "tc_last_error", "tc_device_status", "tc_version"):
+        assert want in names
+
+
+def test_library_exports_every_declared_symbol():
+    lib = ctypes.CDLL(str(_lib.LIB_PATH))
+    for name in declared_symbols():
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+
+
+def test_python_binding_covers_every_declared_symbol():
+    assert sorted(_lib.SIGNATURES) == declared_symbols()
+    assert _lib.load().tc_version() >= 1000
+
+
+def test_every_declaration_cites_the_reference_or_says_it_has_no_counterpart():
+    text = HEADER.read_text()
+    for m in re.finditer(r"/\*(.*?)\*/\s*(?:int|const char\*)\s+(tc_[a-z0-9_]+)\s*\(", text, flags=re.S):
+        comment, name = m.group(1), m.group(2)
+        if name in ("tc_last_error", "tc_version"):
+            continue
+        assert re.search(r"\.(cu|hpp|py|cc)?:?\d+|Makefile:\d+|no counterpart", comment), name
+
+
+@pytest.mark.parametrize(
+    "call, needle",
+    [
+        (lambda l: l.tc_gemm_f16_f32(None, None, None, 128, 128, 64, 64, 64, 128, None), "null"),
+        (lambda l: l.tc_gemm_f16_f32(16, 16, 16, 128, 128, 60, 64, 64, 128, None), "multiple of 8"),
+        (lambda l: l.tc_gemm_f16_f32(16, 16, 16, 0, 128, 64, 64, 64, 128, None), "positive"),
+        (lambda l: l.tc_gemm_f16_f32(16, 16, 16, 128, 128, 64, 32, 64, 128, None), "leading dimension"),
+        (lambda l: l.tc_gemm_f16_f32(18, 16, 16, 128, 128, 64, 64, 64, 128, None), "aligned"),
+        (lambda l: l.tc_b2b_gemm_f16(16, 16, 16, 16, 128, 128, 256, 128, 1, None), "[16,128]"),
+        (lambda l: l.tc_b2b_gemm_f16(16, 16, 16, 16, 128, 100, 128, 128, 1, None), "multiple of 8"),
+        (lambda l: l.tc_flash_attn_fwd_f16(16, 16, 16, 16, None, 1, 1, 128, 128, 72, 128, 1.0, 0, None), "multiple of 16"),
+        (lambda l: l.tc_flash_attn_fwd_f16(16, 16, 16, 16, None, 0, 1, 128, 128, 64, 64, 1.0, 0, None), "positive"),
+        (lambda l: l.tc_flash_attn_fwd_f16(16, 16, 16, 16, None, 1, 1, 128, 128, 64, 64, float("nan"), 0, None), "finite"),
+        (lambda l: l.tc_lstm_cell_f16(16, 16, None, 16, 16, 16, 16, 16, 8, 64, 24, None), "multiple of 16"),
+        (lambda l: l.tc_lstm_cell_f16(16, 16, None, 16, 32, 16, 32, 16, 8, 64, 32, None), "alias"),
+        (lambda l: l.tc_lstm_chain_f16(16, 16, None, 16, 16, 16, 16, 16, 0, 8, 64, 32, None), "steps"),
+    ],
+)
+def test_bad_arguments_return_a_status_and_a_message(call, needle):
+    lib = _lib.load()
+    rc = call(lib)
+    assert rc == -1  # TC_ERR_BAD_ARG
+    assert needle in lib.tc_last_error().decode()
+
+
+def test_scatter_argument_checks():
+    lib = _lib.load()
+    dims = (ctypes.c_int64 * 2)(8, 4)
+    assert lib.tc_scatter_nd(None, 16, 16, 0, dims, 2, 4, 1, 2, None) == -1
+    assert lib.tc_scatter_nd(16, 16, 16, 0, dims, 2, 4, 3, 2, None) == -1  # k > rank
+    assert lib.tc_scatter_nd(16, 16, 16, 0, dims, 2, 4, 1, 3, None) == -1  # elem_bytes
+    assert "elem_bytes" in lib.tc_last_error().decode()
+    assert lib.tc_scatter_nd(16, 16, 16, 0, dims, 2, 0, 1, 2, None) == 0   # n == 0: nothing to do
+
+
+def test_check_raises_with_the_library_message():
+    lib = _lib.load()
+    rc = lib.tc_gemm_f16_f32(None, None, None, 1, 1, 8, 8, 8, 1, None)
+    with pytest.raises(_lib.TiledCudaError) as ei:
+        _lib.check("tc_gemm_f16_f32", rc)
+    assert ei.value.status == -1 and "null" in str(ei.value)

@@ -106,7 +106,8 @@ static int launch_scatter_idx(void* data, const void* updates, const void* indic
 extern "C" int tc_scatter_nd(void* data, const void* updates, const void* indices, int idx_is_int64,
                              const int64_t* dims, int rank, int64_t n, int k, int elem_bytes, tc_stream_t stream) {
     using namespace tcb;
-    TCB_REQUIRE(data && updates && indices && dims, "scatter_nd: null pointer argument");
+    TCB_REQUIRE(data && dims, "scatter_nd: null pointer argument");
+    TCB_REQUIRE(n <= 0 || (updates && indices), "scatter_nd: null pointer argument");
     TCB_REQUIRE(rank >= 1 && rank <= 16, "scatter_nd: rank %d outside [1,16]", rank);
     TCB_REQUIRE(k >= 1 && k <= rank && k <= kMaxIndexRank, "scatter_nd: index tuple length %d outside [1,min(rank,%d)]",
                 k, kMaxIndexRank);
