@@ -114,3 +114,15 @@ def test_two_gloo_ranks_shard_and_gather(ragged):
     assert results[0][1] == 0 and results[0][2] == results[1][1]
     assert results[1][2] == (300 if ragged else 256)
     assert all(r[3] and r[4] for r in results)
+
+
+def test_torch_op_library_registers_the_reference_ops_and_has_no_cpu_kernel():
+    from tiledcuda_b200 import pytiledcuda
+
+    for name in ("scatter_nd", "flash_attention_fwd", "gemm", "back2back_gemm", "lstm_cell", "flash_attn"):
+        assert hasattr(torch.ops.tiledcuda, name)
+    a = torch.zeros(8, 8, dtype=torch.float16)
+    with pytest.raises((NotImplementedError, RuntimeError)):
+        pytiledcuda.gemm(a, a, torch.zeros(8, 8))
+    for name in ("scatter_nd", "flash_attention_fwd", "TiledFlashAttention"):
+        assert hasattr(pytiledcuda, name)
