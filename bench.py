@@ -42,8 +42,9 @@ SEED = 1234  # the seed of the reference's Python tests
 # DRAM bytes (read + write) per launch of the dominant kernel, from the ncu captures summarised under
 # profiles/ (file named per entry). None where no capture exists.
 NCU_TRAFFIC_BYTES: dict[str, int | None] = {
-    "gemm8192": None,
-    "scatter": None,
+    "gemm8192": 1_305_000_000,   # profiles/gemm_8192_ncu.md
+    "scatter": 1_387_700_000,    # profiles/scatter_nd_c5_ncu.md
+    "fa": 2_131_100_000,         # profiles/flash_attn_c3_ncu.md
 }
 
 
@@ -60,36 +61,83 @@ def measured_peaks() -> dict:
 # clocks
 # ----------------------------------------------------------------------------------------------------
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons of one GPU while a timed region runs."""
+    """Samples SM clock, power and throttle reasons of one GPU (read-only NVML queries) every few
+    milliseconds while a timed region runs; falls back to `nvidia-smi -lms` if NVML cannot be loaded."""
 
+    REASONS = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
         self.index = index
+        self.samples: list[tuple[float, int]] = []
+        self.sm_max = None
+        self.power: list[float] = []
+        self._stop = threading.Event()
+        self.thread = None
         self.proc = None
         self.lines: list[str] = []
-        self.thread = None
+
+    def _physical_index(self) -> int:
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [x.strip() for x in vis.split(",") if x.strip()]
+            if self.index < len(ids) and ids[self.index].isdigit():
+                return int(ids[self.index])
+        return self.index
 
     def start(self):
         try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
+        try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self._physical_index())], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
         except OSError:
             self.proc = None
-            return
-        self.thread = threading.Thread(target=self._read, daemon=True)
-        self.thread.start()
+
+    def _poll(self):
+        n = self.nvml
+        while not self._stop.is_set():
+            try:
+                mhz = float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                try:
+                    mask = int(n.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                except Exception:
+                    mask = int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                self.samples.append((mhz, mask))
+                self.power.append(n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0)
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
     def stop(self) -> dict:
+        if getattr(self, "nvml", None) is not None:
+            self._stop.set()
+            self.thread.join(timeout=2)
+            reasons = sorted(name for name, bit in self.REASONS.items() if any(m & bit for _, m in self.samples))
+            sm = [x for x, _ in self.samples]
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_min_mhz": min(sm) if sm else None,
+                    "sm_max_mhz": self.sm_max, "power_w_max": round(max(self.power), 1) if self.power else None,
+                    "samples": len(sm), "reasons": reasons, "source": "nvml"}
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock sampling unavailable"]}
         time.sleep(0.15)
         self.proc.terminate()
         try:
@@ -111,7 +159,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi"}
 
 
 # ----------------------------------------------------------------------------------------------------
@@ -366,12 +414,14 @@ def flush_l2(device, scratch=[None]):
     scratch[0].fill_(1)
 
 
-def time_steps(fn, steps: int, warmup: int, barrier, flush=False, device=None) -> float:
+def time_steps(fn, steps: int, warmup: int, barrier, flush=False, device=None, on_timed_start=None) -> float:
     """Milliseconds per step on the device, CUDA events on the launching stream, barrier + sync on both sides."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     barrier()
+    if on_timed_start is not None:
+        on_timed_start()
     if flush:
         total = 0.0
         for _ in range(steps):
@@ -510,8 +560,8 @@ def main() -> int:
     desc = w.describe()
 
     sampler = ClockSampler(local_rank)
-    sampler.start()
-    ms = time_steps(w.step, args.steps, args.warmup, barrier, flush=bool(desc.get("flush_l2")), device=device)
+    ms = time_steps(w.step, args.steps, args.warmup, barrier, flush=bool(desc.get("flush_l2")), device=device,
+                    on_timed_start=sampler.start)
     clocks = sampler.stop()
     status = _lib.device_status()
 
