@@ -395,6 +395,10 @@ static int check_chain_dims(const char* op, int64_t batch, int64_t rows, int64_t
     return TC_OK;
 }
 
+// Two-tile ping-pong attention kernel (attn.cu), used when there is more than one 128-row tile of queries.
+int launch_attn_pingpong(const void* Q, const void* K, const void* V, void* O, float* lse, int64_t bh, int64_t seq_q,
+                         int64_t seq_kv, int64_t dk, int64_t dv, float scale, bool v_trans, cudaStream_t stream);
+
 }  // namespace tcb
 
 extern "C" int tc_b2b_gemm_f16(const void* A, const void* B, const void* D, void* E, int64_t M, int64_t N, int64_t K,
@@ -419,6 +423,9 @@ extern "C" int tc_flash_attn_fwd_f16(const void* Q, const void* K, const void* V
     TCB_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(V) && aligned16(O), "flash_attn_fwd: pointers must be 16-byte aligned");
     TCB_REQUIRE(isfinite(scale), "flash_attn_fwd: scale is not finite");
     auto* st = static_cast<cudaStream_t>(stream);
+    if (seq_q > kChBM)
+        return launch_attn_pingpong(Q, K, V, O, lse, batch * heads, seq_q, seq_kv, head_dim, head_dim_v, scale,
+                                    v_is_transposed != 0, st);
     if (v_is_transposed)
         return launch_chain<true, true>(Q, K, V, O, lse, batch * heads, seq_q, seq_kv, head_dim, head_dim_v, scale, st);
     return launch_chain<true, false>(Q, K, V, O, lse, batch * heads, seq_q, seq_kv, head_dim, head_dim_v, scale, st);
