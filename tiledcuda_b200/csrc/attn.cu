@@ -236,29 +236,41 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             tc_fence_after_sync();
             const int n_valid = min(kFaBN, p.seq_kv - j * kFaBN);
 
-            // pass 1: row maximum of scale * s
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < kFaBN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_x32(s_addr + static_cast<uint32_t>(c * 32), r);
-                tmem_ld_wait();
-                if (n_valid == kFaBN) {
-                    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+            // all 128 scores of this row into registers (one round trip to TMEM)
+            uint32_t s[128];
+            tmem_ld_x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+            tmem_ld_x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+            tmem_ld_x32(s_addr + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
+            tmem_ld_x32(s_addr + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
+            tmem_ld_wait();
+            if (n_valid < kFaBN) {
+                const float masked = sc >= 0.f ? -INFINITY : INFINITY;  // scale * masked = -inf
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        m0 = fmaxf(m0, __uint_as_float(r[i]) * sc);
-                        m1 = fmaxf(m1, __uint_as_float(r[i + 1]) * sc);
-                        m2 = fmaxf(m2, __uint_as_float(r[i + 2]) * sc);
-                        m3 = fmaxf(m3, __uint_as_float(r[i + 3]) * sc);
-                    }
-                    mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (c * 32 + i < n_valid) mx = fmaxf(mx, __uint_as_float(r[i]) * sc);
-                }
+                for (int i = 0; i < 128; ++i)
+                    if (i >= n_valid) s[i] = __float_as_uint(masked);
             }
+            // row maximum of scale * s: the extreme of the raw scores times the scale
+            float e0 = __uint_as_float(s[0]), e1 = __uint_as_float(s[1]), e2 = __uint_as_float(s[2]), e3 = __uint_as_float(s[3]);
+            if (sc >= 0.f) {
+#pragma unroll
+                for (int i = 4; i < 128; i += 4) {
+                    e0 = fmaxf(e0, __uint_as_float(s[i]));
+                    e1 = fmaxf(e1, __uint_as_float(s[i + 1]));
+                    e2 = fmaxf(e2, __uint_as_float(s[i + 2]));
+                    e3 = fmaxf(e3, __uint_as_float(s[i + 3]));
+                }
+                e0 = fmaxf(fmaxf(e0, e1), fmaxf(e2, e3));
+            } else {
+#pragma unroll
+                for (int i = 4; i < 128; i += 4) {
+                    e0 = fminf(e0, __uint_as_float(s[i]));
+                    e1 = fminf(e1, __uint_as_float(s[i + 1]));
+                    e2 = fminf(e2, __uint_as_float(s[i + 2]));
+                    e3 = fminf(e3, __uint_as_float(s[i + 3]));
+                }
+                e0 = fminf(fminf(e0, e1), fminf(e2, e3));
+            }
+            const float mx = e0 * sc;
             float factor = 1.f;
             if (j == 0) {
                 m_used = mx;
@@ -279,37 +291,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     tmem_st_x16(o_addr + static_cast<uint32_t>(c * 16), r);
                 }
             }
-            // pass 2: exponentials, row sum, fp16 P written over the low half of the score columns
-            float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < kFaBN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_x32(s_addr + static_cast<uint32_t>(c * 32), r);
-                tmem_ld_wait();
-                uint32_t packed[16];
-                if (n_valid == kFaBN) {
+            // exponentials, row sum, fp16 P written over the low half of the score columns
+            const float neg_m = -m_used;
+            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float a = fast_exp2(fmaf(__uint_as_float(r[2 * i]), sc, -m_used));
-                        const float b = fast_exp2(fmaf(__uint_as_float(r[2 * i + 1]), sc, -m_used));
-                        sum0 += a;
-                        sum1 += b;
-                        packed[i] = pack_half2(a, b);
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float a = (c * 32 + 2 * i < n_valid) ? fast_exp2(fmaf(__uint_as_float(r[2 * i]), sc, -m_used)) : 0.f;
-                        const float b =
-                            (c * 32 + 2 * i + 1 < n_valid) ? fast_exp2(fmaf(__uint_as_float(r[2 * i + 1]), sc, -m_used)) : 0.f;
-                        sum0 += a;
-                        sum1 += b;
-                        packed[i] = pack_half2(a, b);
-                    }
-                }
-                tmem_st_x16(s_addr + static_cast<uint32_t>(c * 16), packed);
+            for (int i = 0; i < 64; i += 2) {
+                const float a = fast_exp2(fmaf(__uint_as_float(s[2 * i]), sc, neg_m));
+                const float b = fast_exp2(fmaf(__uint_as_float(s[2 * i + 1]), sc, neg_m));
+                const float c2 = fast_exp2(fmaf(__uint_as_float(s[2 * i + 2]), sc, neg_m));
+                const float d2 = fast_exp2(fmaf(__uint_as_float(s[2 * i + 3]), sc, neg_m));
+                sum0 += a;
+                sum1 += b;
+                sum2 += c2;
+                sum3 += d2;
+                s[i] = pack_half2(a, b);
+                s[i + 1] = pack_half2(c2, d2);
             }
-            l_sum += sum0 + sum1;
+            tmem_st_x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+            tmem_st_x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+            const float sum01 = (sum0 + sum1) + (sum2 + sum3);
+            l_sum += sum01;
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
