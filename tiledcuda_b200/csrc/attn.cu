@@ -1,16 +1,20 @@
-// FlashAttention-2 forward for sequences longer than one tile: two 128-row Q tiles per CTA, ping-pong.
+// FlashAttention-2 forward for sequences longer than one tile: two 128-row Q tiles per CTA.
 //
-//   warp 0       TMA producer: both Q tiles once, then K_0, V_0, K_1, V_1, ... through one 4-stage ring;
-//   warp 1       tcgen05.mma issuer. For each KV block j and each tile t: O_t += P_t(j) V_j (A operand read
-//                from TMEM), then S_t = Q_t K_{j+1}^T. While tile 0's scores are being exponentiated the
-//                tensor pipe works on tile 1 and vice versa;
-//   warps 2..5   softmax warpgroup of tile 0, warps 6..9 of tile 1: one thread per query row. tcgen05.ld
-//                the fp32 scores, online softmax with fp32 running maximum and sum (exp2, scale folded
+//   warp 0       TMA producer: both Q tiles once, then K_0, V_0, K_1, V_1, ... (128 KV rows each) through
+//                one 4-stage ring;
+//   warps 1, 2   tcgen05.mma issuers, one per Q tile (their instruction streams touch disjoint TMEM, so no
+//                order is needed between them). Scores are produced and consumed in half blocks of 64 KV
+//                rows; each tile owns two 64-column score buffers in TMEM. For half block g the issuer of tile t issues
+//                O_t += P_t(g) V(g) (A operand read from TMEM) and then S_t(g+2) = Q_t K(g+2)^T into the
+//                buffer P_t(g) just vacated, so the scores of the next half block are ready while the
+//                softmax warps still work on the current one;
+//   warps 4..7   softmax warpgroup of tile 0, warps 8..11 of tile 1: one thread per query row. tcgen05.ld
+//                64 fp32 scores, online softmax with fp32 running maximum and sum (exp2, scale folded
 //                in), round to fp16 and tcgen05.st P over the columns the scores came from: P never
 //                leaves TMEM. O_t stays in TMEM, is rescaled only when the row maximum grew by more
-//                than 2^8, and is normalised once at the end.
-// TMEM: S_0 | S_1 | O_0 | O_1, 128 columns each. tcgen05.mma instructions of one CTA execute in issue
-// order, so S_t(j+1) may overwrite P_t(j) right after P_t(j) V_j was issued.
+//                than 2^8 (after waiting for the PV product in flight), and is normalised once at the end.
+// TMEM: S_0a S_0b | S_1a S_1b | O_0 | O_1 (64, 64, 64, 64, 128, 128 columns). tcgen05.mma instructions
+// of one CTA execute in issue order, so S_t(g+2) may overwrite P_t(g) right after P_t(g) V(g) was issued.
 //
 // Stands in for flash_attention (src/kernels/flash_attn.cu:134-312), which holds one 64-row tile per
 // CTA, re-loads Q for every KV block, keeps its statistics in fp16 and divides O by the running sum in
@@ -25,7 +29,7 @@ namespace tcb {
 constexpr int kFaBM = 128;
 constexpr int kFaBN = 128;
 constexpr int kFaStages = 4;
-constexpr int kFaThreads = 320;
+constexpr int kFaThreads = 384;
 constexpr int kFaTile = 128 * 128 * 2;
 constexpr int kFaChunk = 128 * 64 * 2;
 constexpr int kFaSmem = kFaTile * (2 + kFaStages) + 256 + 1024;
@@ -54,9 +58,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     uint64_t* bar_q_full = bars;                        // 2
     uint64_t* bar_kv_full = bars + 2;                   // kFaStages
     uint64_t* bar_kv_empty = bar_kv_full + kFaStages;   // kFaStages
-    uint64_t* bar_s_full = bar_kv_empty + kFaStages;    // 2
-    uint64_t* bar_p_full = bar_s_full + 2;              // 2
-    uint64_t* bar_o_full = bar_p_full + 2;              // 2
+    uint64_t* bar_s_full = bar_kv_empty + kFaStages;    // [tile][buffer]: 4
+    uint64_t* bar_p_full = bar_s_full + 4;              // [tile][buffer]: 4
+    uint64_t* bar_pv_done = bar_p_full + 4;             // [tile]: 2
+    uint64_t* bar_o_full = bar_pv_done + 2;             // [tile]: 2
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_o_full + 2);
     volatile uint32_t* abort_word = tmem_slot + 1;
 
@@ -64,7 +69,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const int lane = threadIdx.x & 31;
     const int q0 = blockIdx.x * (2 * kFaBM);
     const int bh = blockIdx.y;
-    const int n_blocks = (p.seq_kv + kFaBN - 1) / kFaBN;
+    const int n_blocks = (p.seq_kv + kFaBN - 1) / kFaBN;   // 128-row K / V blocks (TMA granularity)
+    const int n_halves = (p.seq_kv + 63) / 64;             // 64-row half blocks (score granularity)
     const int k_chunks = (p.dk + 63) / 64;
     const int v_chunks = (p.dv + 63) / 64;
     const int k_steps = p.dk / 16;
@@ -73,13 +79,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     if (threadIdx.x == 0) {
         for (int t = 0; t < 2; ++t) {
             mbar_init(&bar_q_full[t], 1);
-            mbar_init(&bar_s_full[t], 1);
-            mbar_init(&bar_p_full[t], 4);
+            mbar_init(&bar_pv_done[t], 1);
             mbar_init(&bar_o_full[t], 1);
+        }
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(&bar_s_full[i], 1);
+            mbar_init(&bar_p_full[i], 4);
         }
         for (int s = 0; s < kFaStages; ++s) {
             mbar_init(&bar_kv_full[s], 1);
-            mbar_init(&bar_kv_empty[s], 1);
+            mbar_init(&bar_kv_empty[s], two_tiles ? 2 : 1);  // one release per MMA warp in use
         }
         *abort_word = 0;
         fence_barrier_init();
@@ -135,125 +144,133 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            const uint32_t idesc_s = make_idesc_f16_f32(kFaBM, kFaBN, false, false);
+    } else if (warp == 1 || warp == 2) {
+        // ---------------- MMA issuers: warp 1 drives tile 0, warp 2 drives tile 1 ----------------
+        // One lane runs the whole role: a commit tracks the MMAs of the thread that executes it, and a
+        // role that never re-converges with its idle lanes pays no divergence cost inside the loop.
+        const int t = warp - 1;
+        constexpr bool leader = true;
+        if (lane == 0 && (t == 0 || two_tiles)) {
+            const uint32_t idesc_s = make_idesc_f16_f32(kFaBM, 64, false, false);
             const uint32_t idesc_o = make_idesc_f16_f32(kFaBM, p.dv, false, !kVTrans);
-            const int n_tiles = two_tiles ? 2 : 1;
 
             auto kv_stage = [](int e) { return e % kFaStages; };
             auto kv_phase = [](int e) { return static_cast<uint32_t>((e / kFaStages) & 1); };
 
-            // S_t = Q_t K_j^T
-            auto issue_s = [&](int t, int j) {
-                const uint32_t q_addr = smem_u32(s_q + t * kFaTile);
-                const uint32_t k_addr = smem_u32(s_kv + kv_stage(2 * j) * kFaTile);
-                const uint32_t d = tmem_base + static_cast<uint32_t>(t * kFaBN);
-                for (int kk = 0; kk < k_steps; ++kk) {
-                    const uint32_t off = static_cast<uint32_t>((kk >> 2) * kFaChunk + (kk & 3) * 32);
-                    umma_f16_ss(d, make_smem_desc_sw128(q_addr + off, 16, 1024), make_smem_desc_sw128(k_addr + off, 16, 1024),
-                                idesc_s, kk != 0);
-                }
-                umma_commit(&bar_s_full[t]);
-            };
-            // O_t += P_t V_j, P_t read from TMEM columns [t*128, t*128 + 64)
-            auto issue_pv = [&](int t, int j) {
-                const uint32_t v_addr = smem_u32(s_kv + kv_stage(2 * j + 1) * kFaTile);
-                const uint32_t d = tmem_base + static_cast<uint32_t>(256 + t * 128);
-                const uint32_t a = tmem_base + static_cast<uint32_t>(t * kFaBN);
-                for (int kk = 0; kk < kFaBN / 16; ++kk) {
-                    uint64_t b_desc;
-                    if (kVTrans) {
-                        const uint32_t b_off = static_cast<uint32_t>((kk >> 2) * (p.dv * 128) + (kk & 3) * 32);
-                        b_desc = make_smem_desc_sw128(v_addr + b_off, 16, 1024);
-                    } else {
-                        b_desc = make_smem_desc_sw128(v_addr + static_cast<uint32_t>(kk * 2048), kFaChunk, 1024);
+            const uint32_t desc_hi = smem_desc_hi_sw128(1024);
+            constexpr uint32_t kTileStep = static_cast<uint32_t>(kFaTile) >> 4;  // descriptor address units per tile
+            const uint32_t q_lo = smem_desc_lo(smem_u32(s_q), 16) + static_cast<uint32_t>(t) * kTileStep;
+            const uint32_t kv_lo0 = smem_desc_lo(smem_u32(s_kv), 16);
+            const uint32_t v_lbo_word = kVTrans ? 0u : ((static_cast<uint32_t>(kFaChunk) >> 4) - 1u) << 16;  // LBO 16 -> kFaChunk
+            const uint32_t v_half_step = kVTrans ? static_cast<uint32_t>(p.dv * 128) >> 4 : (64u * 128u) >> 4;
+            const uint32_t v_k_step = kVTrans ? 2u : 2048u >> 4;
+            const uint32_t tmem_s = tmem_base + static_cast<uint32_t>(t * 128);
+            const uint32_t tmem_o = tmem_base + static_cast<uint32_t>(256 + t * 128);
+
+            // S_t(g) = Q_t K(g)^T for the 64 KV rows of half block g, into score buffer g & 1
+            auto issue_s = [&](int g) {
+                const int h = g & 1;
+                const uint32_t b_lo = kv_lo0 + static_cast<uint32_t>(kv_stage(2 * (g >> 1))) * kTileStep + static_cast<uint32_t>(h * ((64 * 128) >> 4));
+                const uint32_t d = tmem_s + static_cast<uint32_t>(h * 64);
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    if (kk < k_steps) {
+                        const uint32_t off = static_cast<uint32_t>(((kk >> 2) * kFaChunk + (kk & 3) * 32) >> 4);
+                        if (leader)
+                            umma_f16_ss(d, smem_desc_join(q_lo + off, desc_hi), smem_desc_join(b_lo + off, desc_hi), idesc_s, kk != 0);
                     }
-                    umma_f16_ts(d, a + static_cast<uint32_t>(kk * 8), b_desc, idesc_o, (j | kk) != 0);
                 }
+                if (leader) umma_commit(&bar_s_full[t * 2 + h]);
+            };
+            // O_t += P_t(g) V(g); P_t(g) is read from the first 32 columns of score buffer g & 1
+            auto issue_pv = [&](int g) {
+                const int h = g & 1;
+                const uint32_t b_lo = kv_lo0 + static_cast<uint32_t>(kv_stage(2 * (g >> 1) + 1)) * kTileStep + v_lbo_word +
+                                      static_cast<uint32_t>(h) * v_half_step;
+                const uint32_t a = tmem_s + static_cast<uint32_t>(h * 64);
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    if (leader)
+                        umma_f16_ts(tmem_o, a + static_cast<uint32_t>(kk * 8),
+                                    smem_desc_join(b_lo + static_cast<uint32_t>(kk) * v_k_step, desc_hi), idesc_o, (g | kk) != 0);
+                }
+                if (leader) umma_commit(&bar_pv_done[t]);
             };
 
-            bool ok = mbar_wait(&bar_q_full[0], 0, abort_word, kDevTimeoutMma) &&
+            // prologue: the first two half blocks of scores (both from K_0)
+            bool ok = mbar_wait(&bar_q_full[t], 0, abort_word, kDevTimeoutMma) &&
                       mbar_wait(&bar_kv_full[kv_stage(0)], kv_phase(0), abort_word, kDevTimeoutMma);
             if (ok) {
                 tc_fence_after_sync();
-                issue_s(0, 0);
-                if (n_tiles == 2) {
-                    ok = mbar_wait(&bar_q_full[1], 0, abort_word, kDevTimeoutMma);
-                    if (ok) {
-                        tc_fence_after_sync();
-                        issue_s(1, 0);
-                    }
-                }
-                umma_commit(&bar_kv_empty[kv_stage(0)]);
+                issue_s(0);
+                if (n_halves > 1) issue_s(1);
+                if (leader) umma_commit(&bar_kv_empty[kv_stage(0)]);
             }
-            for (int j = 0; ok && j < n_blocks; ++j) {
-                const bool has_next = j + 1 < n_blocks;
-                if (!mbar_wait(&bar_kv_full[kv_stage(2 * j + 1)], kv_phase(2 * j + 1), abort_word, kDevTimeoutMma)) break;
-                for (int t = 0; t < n_tiles; ++t) {
-                    if (!mbar_wait(&bar_p_full[t], static_cast<uint32_t>(j & 1), abort_word, kDevTimeoutMma)) {
-                        ok = false;
+            for (int g = 0; ok && g < n_halves; ++g) {
+                const int j = g >> 1;
+                const bool more_s = g + 2 < n_halves;
+                if ((g & 1) == 0) {
+                    if (!mbar_wait(&bar_kv_full[kv_stage(2 * j + 1)], kv_phase(2 * j + 1), abort_word, kDevTimeoutMma)) break;
+                    if (more_s &&
+                        !mbar_wait(&bar_kv_full[kv_stage(2 * j + 2)], kv_phase(2 * j + 2), abort_word, kDevTimeoutMma))
                         break;
-                    }
-                    tc_fence_after_sync();
-                    issue_pv(t, j);
-                    if (t == n_tiles - 1) umma_commit(&bar_kv_empty[kv_stage(2 * j + 1)]);
-                    if (has_next) {
-                        if (t == 0 &&
-                            !mbar_wait(&bar_kv_full[kv_stage(2 * j + 2)], kv_phase(2 * j + 2), abort_word, kDevTimeoutMma)) {
-                            ok = false;
-                            break;
-                        }
-                        tc_fence_after_sync();
-                        issue_s(t, j + 1);
-                        if (t == n_tiles - 1) umma_commit(&bar_kv_empty[kv_stage(2 * j + 2)]);
-                    } else {
-                        umma_commit(&bar_o_full[t]);
-                    }
+                }
+                if (!mbar_wait(&bar_p_full[t * 2 + (g & 1)], static_cast<uint32_t>((g >> 1) & 1), abort_word, kDevTimeoutMma)) break;
+                tc_fence_after_sync();
+                issue_pv(g);
+                if (more_s) issue_s(g + 2);
+                if (leader) {
+                    if (g == n_halves - 1) umma_commit(&bar_o_full[t]);
+                    // V_j is free once its second half (or the last half block) has been issued
+                    if ((g & 1) == 1 || g == n_halves - 1) umma_commit(&bar_kv_empty[kv_stage(2 * j + 1)]);
+                    // K of block (g+2)/2 is free once its last half block of scores has been issued
+                    if (more_s && (((g + 2) & 1) == 1 || g + 2 == n_halves - 1))
+                        umma_commit(&bar_kv_empty[kv_stage(2 * ((g + 2) >> 1))]);
                 }
             }
         }
         __syncwarp();
+    } else if (warp == 3) {
+        // idle: keeps the softmax warpgroups aligned to TMEM lane quarters
     } else {
         // ---------------- softmax warpgroups: one thread per query row ----------------
-        const int t = (warp - 2) >> 2;   // tile of this warpgroup
+        const int t = (warp - 4) >> 2;   // tile of this warpgroup
         const int quarter = warp & 3;
         const int row = q0 + t * kFaBM + quarter * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        const uint32_t s_addr = tmem_base + lane_base + static_cast<uint32_t>(t * kFaBN);
+        const uint32_t s_base = tmem_base + lane_base + static_cast<uint32_t>(t * 128);
         const uint32_t o_addr = tmem_base + lane_base + static_cast<uint32_t>(256 + t * 128);
         const float sc = p.scale_log2;
         float m_used = -INFINITY;
         float l_sum = 0.f;
         bool ok = (t == 0) || two_tiles;
 
-        for (int j = 0; ok && j < n_blocks; ++j) {
-            if (!mbar_wait_warp(&bar_s_full[t], static_cast<uint32_t>(j & 1), abort_word, kDevTimeoutSoftmax)) {
+        for (int g = 0; ok && g < n_halves; ++g) {
+            const int h = g & 1;
+            if (!mbar_wait_warp(&bar_s_full[t * 2 + h], static_cast<uint32_t>((g >> 1) & 1), abort_word, kDevTimeoutSoftmax)) {
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
-            const int n_valid = min(kFaBN, p.seq_kv - j * kFaBN);
+            const uint32_t s_addr = s_base + static_cast<uint32_t>(h * 64);
+            const int n_valid = min(64, p.seq_kv - g * 64);
 
-            // all 128 scores of this row into registers (one round trip to TMEM)
-            uint32_t s[128];
+            // the 64 scores of this row and half block into registers
+            uint32_t s[64];
             tmem_ld_x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
             tmem_ld_x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-            tmem_ld_x32(s_addr + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
-            tmem_ld_x32(s_addr + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
             tmem_ld_wait();
-            if (n_valid < kFaBN) {
+            if (n_valid < 64) {
                 const float masked = sc >= 0.f ? -INFINITY : INFINITY;  // scale * masked = -inf
 #pragma unroll
-                for (int i = 0; i < 128; ++i)
+                for (int i = 0; i < 64; ++i)
                     if (i >= n_valid) s[i] = __float_as_uint(masked);
             }
             // row maximum of scale * s: the extreme of the raw scores times the scale
             float e0 = __uint_as_float(s[0]), e1 = __uint_as_float(s[1]), e2 = __uint_as_float(s[2]), e3 = __uint_as_float(s[3]);
             if (sc >= 0.f) {
 #pragma unroll
-                for (int i = 4; i < 128; i += 4) {
+                for (int i = 4; i < 64; i += 4) {
                     e0 = fmaxf(e0, __uint_as_float(s[i]));
                     e1 = fmaxf(e1, __uint_as_float(s[i + 1]));
                     e2 = fmaxf(e2, __uint_as_float(s[i + 2]));
@@ -262,7 +279,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 e0 = fmaxf(fmaxf(e0, e1), fmaxf(e2, e3));
             } else {
 #pragma unroll
-                for (int i = 4; i < 128; i += 4) {
+                for (int i = 4; i < 64; i += 4) {
                     e0 = fminf(e0, __uint_as_float(s[i]));
                     e1 = fminf(e1, __uint_as_float(s[i + 1]));
                     e2 = fminf(e2, __uint_as_float(s[i + 2]));
@@ -272,15 +289,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
             const float mx = e0 * sc;
             float factor = 1.f;
-            if (j == 0) {
+            if (g == 0) {
                 m_used = mx;
             } else if (mx > m_used + kFaRescaleThreshold) {
                 factor = fast_exp2(m_used - mx);
                 m_used = mx;
             }
-            // s_full of block j was committed after P_t(j-1) V_{j-1}: O_t is quiescent here
             l_sum *= factor;
             if (__any_sync(0xffffffffu, factor != 1.f)) {
+                // O_t may still be the target of P_t(g-1) V(g-1): wait for it. Seeing s_full of half block g
+                // means the product of half block g-2 is complete, so the parity is unambiguous.
+                if (!mbar_wait_warp(&bar_pv_done[t], static_cast<uint32_t>((g - 1) & 1), abort_word, kDevTimeoutSoftmax)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
 #pragma unroll 1
                 for (int c = 0; c < p.dv / 16; ++c) {
                     uint32_t r[16];
@@ -291,11 +314,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     tmem_st_x16(o_addr + static_cast<uint32_t>(c * 16), r);
                 }
             }
-            // exponentials, row sum, fp16 P written over the low half of the score columns
+            // exponentials, row sum, fp16 P written over the first 32 score columns
             const float neg_m = -m_used;
             float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
-            for (int i = 0; i < 64; i += 2) {
+            for (int i = 0; i < 32; i += 2) {
                 const float a = fast_exp2(fmaf(__uint_as_float(s[2 * i]), sc, neg_m));
                 const float b = fast_exp2(fmaf(__uint_as_float(s[2 * i + 1]), sc, neg_m));
                 const float c2 = fast_exp2(fmaf(__uint_as_float(s[2 * i + 2]), sc, neg_m));
@@ -308,13 +331,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 s[i + 1] = pack_half2(c2, d2);
             }
             tmem_st_x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-            tmem_st_x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-            const float sum01 = (sum0 + sum1) + (sum2 + sum3);
-            l_sum += sum01;
+            l_sum += (sum0 + sum1) + (sum2 + sum3);
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bar_p_full[t]);
+            if (lane == 0) mbar_arrive(&bar_p_full[t * 2 + h]);
         }
 
         // ---------------- epilogue ----------------

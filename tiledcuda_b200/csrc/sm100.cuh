@@ -76,17 +76,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait for the phase with the given parity. Returns false when another role has aborted
-// or when the limit ran out (then it records `code` in the CTA's abort word).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word,
-                                          uint32_t code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+// Bounded waits. The common case, a phase that is already complete or completes within a few polls, must
+// cost no more than the poll itself (about a dozen cycles): the fast path is a single try_wait and a
+// uniform branch, and everything that needs a loop, the clock or the abort word lives in a separate
+// non-inlined function, so that the caller carries none of its control flow.
+//
+// mbar_wait: one thread. Returns false when another role has aborted or when the limit ran out (then it
+// records `code` in the CTA's abort word).
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word,
+                                            uint32_t code) {
     uint32_t it = 0;
+    uint64_t t0 = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if ((++it & 0xffu) == 0) {
+        if ((++it & 0xfffu) == 0) {
             if (*abort_word != 0) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > kWaitLimitNs) {
                 *abort_word = code;
                 return false;
             }
@@ -95,12 +102,43 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     return true;
 }
 
-// The same wait made warp-uniform: every lane polls, and the warp proceeds only if all lanes saw the phase
-// complete. Warps that go on to warp-collective instructions (tcgen05.ld / st, votes) use this one, so
-// that a timeout can never leave part of a warp behind.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word,
+                                          uint32_t code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_word, code);
+}
+
+// mbar_wait_warp: a whole converged warp; every lane polls (so every lane acquires the phase) and the
+// warp leaves together, which keeps a timeout from leaving part of a warp behind before a
+// warp-collective instruction (tcgen05.ld / st, votes).
+static __device__ __noinline__ bool mbar_wait_warp_slow(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word,
+                                                 uint32_t code) {
+    uint32_t it = 0;
+    uint64_t t0 = 0;
+    while (!__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) {
+        if ((++it & 0xfffu) == 0) {
+            uint32_t give_up = 0;
+            if (*abort_word != 0) {
+                give_up = 1;
+            } else {
+                const uint64_t now = global_timer_ns();
+                if (t0 == 0) {
+                    t0 = now;
+                } else if (now - t0 > kWaitLimitNs) {
+                    *abort_word = code;
+                    give_up = 1;
+                }
+            }
+            if (__any_sync(0xffffffffu, give_up)) return false;
+        }
+    }
+    return true;
+}
+
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word,
                                                uint32_t code) {
-    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_word, code)) != 0;
+    if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+    return mbar_wait_warp_slow(bar, parity, abort_word, code);
 }
 
 // ---- TMA -----------------------------------------------------------------------------------------
@@ -176,6 +214,21 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
     d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;      // bits [32,46): stride byte offset / 16
     d |= static_cast<uint64_t>(1) << 46;                               // bits [46,48): descriptor version 1
     d |= static_cast<uint64_t>(2) << 61;                               // bits [61,64): 128-byte swizzle
+    return d;
+}
+
+// The same descriptor split into its two 32-bit words. Only the low word depends on the address, so an
+// issuing thread can build the high word once and form each descriptor with one add: stepping the start
+// address by `bytes` adds bytes / 16 to the low word (no carry out of the 14-bit field below 256 KiB).
+__device__ __forceinline__ uint32_t smem_desc_hi_sw128(uint32_t sbo_bytes) {
+    return ((sbo_bytes >> 4) & 0x3fffu) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+    return ((smem_addr & 0x3ffffu) >> 4) | (((lbo_bytes >> 4) & 0x3fffu) << 16);
+}
+__device__ __forceinline__ uint64_t smem_desc_join(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
     return d;
 }
 
