@@ -229,6 +229,10 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, float* C, i
     return TC_OK;
 }
 
+// 256x256 tiles on CTA pairs (gemm_pair.cu); tb must have been encoded with a 64 x 128 box.
+int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int M, int N, int K, int64_t ldc,
+                     const DeviceInfo* dev, cudaStream_t stream);
+
 }  // namespace tcb
 
 extern "C" int tc_gemm_f16_f32(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
@@ -247,10 +251,13 @@ extern "C" int tc_gemm_f16_f32(const void* A, const void* B, void* C, int64_t M,
     const DeviceInfo* dev = nullptr;
     if (int rc = current_device(&dev)) return rc;
 
-    // Narrow problems take the 128-column tile so that more CTAs are busy.
+    // Large problems run 256x256 tiles on CTA pairs; narrow or small ones take lone CTAs with 128x256 or
+    // 128x128 tiles so that more SMs are busy.
+    const int64_t tiles_pair = ((M + 255) / 256) * ((N + 255) / 256);
+    const bool use_pair = tiles_pair >= dev->sm_count / 2;
     const int64_t tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
-    const bool use128 = (N <= 128) || (tiles256 < dev->sm_count);
-    const uint32_t bn = use128 ? 128u : 256u;
+    const bool use128 = !use_pair && ((N <= 128) || (tiles256 < dev->sm_count));
+    const uint32_t bn = (use128 || use_pair) ? 128u : 256u;
 
     CUtensorMap ta, tb;
     {
@@ -266,6 +273,7 @@ extern "C" int tc_gemm_f16_f32(const void* A, const void* B, void* C, int64_t M,
         if (int rc = encode_tmap_f16_sw128(&tb, B, 2, dims, strides, box)) return rc;
     }
     auto* st = static_cast<cudaStream_t>(stream);
+    if (use_pair) return launch_gemm_pair(ta, tb, static_cast<float*>(C), (int)M, (int)N, (int)K, ldc, dev, st);
     if (use128)
         return launch_gemm<128, 6>(ta, tb, static_cast<float*>(C), (int)M, (int)N, (int)K, ldc, dev, st);
     return launch_gemm<256, 4>(ta, tb, static_cast<float*>(C), (int)M, (int)N, (int)K, ldc, dev, st);

@@ -1,0 +1,238 @@
+// GEMM on CTA pairs: C[M,N] (fp32) = A[M,K] (fp16) * B (fp16 column-major [K,N] = [N,K] rows), 256x256
+// output tiles computed by two CTAs (a cluster of two, one per SM) with tcgen05.mma.cta_group::2.
+//
+// Each CTA of a pair loads its own 128 rows of A and its own 128 of the 256 B rows per 64-wide K block
+// (32 KiB per stage instead of 48 KiB for a lone CTA, so six stages fit and B crosses the L2-to-SM
+// fabric once per pair instead of once per CTA). The leader CTA (rank 0) issues the MMAs for both;
+// each CTA keeps its 128 accumulator rows in its own TMEM, double-buffered, and runs its own epilogue.
+//   warp 0      TMA producer (both CTAs): loads land in the issuing CTA's shared memory and complete on
+//               the LEADER's full barrier (no multicast: every byte is fetched by the CTA that uses it);
+//   warp 1      TMEM owner (both CTAs); in the leader also the MMA issuer. After each K block it
+//               commits to the empty barrier of both CTAs, after each tile to both accumulator-full barriers;
+//   warps 2..5  epilogue (both CTAs): tcgen05.ld, fp32 stores, then an arrive on the leader's
+//               accumulator-empty barrier (eight arrivals per tile: four warps in each CTA).
+// All waits are bounded; the two CTAs meet at a cluster barrier before either frees TMEM or exits.
+//
+// Stands in for the same reference code as gemm.cu (examples/cpp/01_gemm/02_gemm_all_mem/gemm.hpp:92-155).
+#include "host.h"
+#include "sm100.cuh"
+
+namespace tcb {
+
+constexpr int kPairBM = 128;      // rows per CTA (256 per pair)
+constexpr int kPairBN = 256;      // columns per pair tile (128 B rows loaded per CTA)
+constexpr int kPairBK = 64;
+constexpr int kPairStages = 6;
+constexpr int kPairThreads = 192;
+constexpr int kPairABytes = kPairBM * kPairBK * 2;
+constexpr int kPairBBytes = (kPairBN / 2) * kPairBK * 2;
+constexpr int kPairStageBytes = kPairABytes + kPairBBytes;
+constexpr int kPairSmem = kPairStages * kPairStageBytes + 256 + 1024;
+constexpr int kPairGroupM = 8;    // pair-tiles (256 rows each) per rasterisation group
+
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+    const int per_group = kPairGroupM * tiles_n;
+    const int group = tile / per_group;
+    const int first_m = group * kPairGroupM;
+    const int rows = min(kPairGroupM, tiles_m - first_m);
+    const int in_group = tile - group * per_group;
+    tm = first_m + in_group % rows;
+    tn = in_group / rows;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 float* __restrict__ C, int M, int N, int K, int64_t ldc, int tiles_m, int tiles_n, uint32_t* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = align_smem_1024(smem_raw);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + kPairStages * kPairABytes;
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);  // used in the leader
+    uint64_t* bar_empty = bar_full + kPairStages;      // one per CTA
+    uint64_t* bar_acc_full = bar_empty + kPairStages;  // one per CTA
+    uint64_t* bar_acc_empty = bar_acc_full + 2;        // used in the leader
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_acc_empty + 2);
+    volatile uint32_t* abort_word = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();   // 0 = leader
+    const uint32_t peer = rank ^ 1u;
+    const int pair = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+    const int num_tiles = tiles_m * tiles_n;
+    const int k_blocks = (K + kPairBK - 1) / kPairBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPairStages; ++s) {
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&bar_acc_full[a], 1);
+            mbar_init(&bar_acc_empty[a], 8);  // four epilogue warps in each CTA of the pair
+        }
+        *abort_word = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    cluster_sync_all();   // barriers of both CTAs are initialised before anyone signals across the pair
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_a);
+            tma_prefetch_desc(&tmap_b);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                int tm, tn;
+                pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+                const int row_a = tm * (2 * kPairBM) + static_cast<int>(rank) * kPairBM;
+                const int row_b = tn * kPairBN + static_cast<int>(rank) * (kPairBN / 2);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&bar_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) {
+                        ok = false;
+                        break;
+                    }
+                    // the leader's full barrier counts the bytes of both CTAs
+                    const uint32_t full_addr = map_to_cta(smem_u32(&bar_full[stage]), 0);
+                    if (rank == 0) mbar_arrive_expect_tx(&bar_full[stage], 2 * kPairStageBytes);
+                    tma_load_2d_pair(smem_a + stage * kPairABytes, &tmap_a, full_addr, kb * kPairBK, row_a);
+                    tma_load_2d_pair(smem_b + stage * kPairBBytes, &tmap_b, full_addr, kb * kPairBK, row_b);
+                    if (++stage == kPairStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc_f16_f32(2 * kPairBM, kPairBN, false, false);
+            const uint32_t desc_hi = smem_desc_hi_sw128(1024);
+            const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem_a), 16);
+            const uint32_t b_lo0 = smem_desc_lo(smem_u32(smem_b), 16);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                if (!mbar_wait(&bar_acc_empty[acc], acc_phase ^ 1u, abort_word, kDevTimeoutMma)) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kPairBN);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&bar_full[stage], phase, abort_word, kDevTimeoutMma)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (kPairABytes >> 4);
+                    const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (kPairBBytes >> 4);
+#pragma unroll
+                    for (int k = 0; k < kPairBK / 16; ++k)
+                        umma_f16_ss_pair(d_tmem, smem_desc_join(a_lo + static_cast<uint32_t>(k * 2), desc_hi),
+                                         smem_desc_join(b_lo + static_cast<uint32_t>(k * 2), desc_hi), idesc, (kb | k) != 0);
+                    // the stage is free in both CTAs once these MMAs have read it
+                    umma_commit_pair(smem_u32(&bar_empty[stage]));
+                    umma_commit_pair(map_to_cta(smem_u32(&bar_empty[stage]), 1));
+                    if (++stage == kPairStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                umma_commit_pair(smem_u32(&bar_acc_full[acc]));
+                umma_commit_pair(map_to_cta(smem_u32(&bar_acc_full[acc]), 1));
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue (both CTAs): TMEM -> registers -> global ----------------
+        const int quarter = warp & 3;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
+        for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+            int tm, tn;
+            pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            if (!mbar_wait_warp(&bar_acc_full[acc], acc_phase, abort_word, kDevTimeoutEpilogue)) break;
+            tc_fence_after_sync();
+            const int row = tm * (2 * kPairBM) + static_cast<int>(rank) * kPairBM + quarter * 32 + lane;
+            const int col0 = tn * kPairBN;
+            float* crow = C + static_cast<int64_t>(row) * ldc;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * kPairBN);
+#pragma unroll 1
+            for (int c = 0; c < kPairBN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_x32(taddr + static_cast<uint32_t>(c * 32), r);
+                tmem_ld_wait();
+                const int col = col0 + c * 32;
+                if (row < M) {
+                    if (vec_ok && col + 32 <= N) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                            __stcs(reinterpret_cast<float4*>(crow + col) + j, v);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col + j < N) crow[col + j] = __uint_as_float(r[j]);
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bar_acc_empty[acc]), 0));
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
+        }
+    }
+
+    // ---------------- teardown: neither CTA frees TMEM or exits while its peer may still touch it ----------------
+    tc_fence_before_sync();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+    if (threadIdx.x == 0 && *abort_word != 0) atomicMax(status, *abort_word);
+}
+
+int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int M, int N, int K, int64_t ldc,
+                     const DeviceInfo* dev, cudaStream_t stream) {
+    static bool configured[64] = {};
+    if (!configured[dev->device]) {
+        TCB_CUDA(cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem));
+        configured[dev->device] = true;
+    }
+    const int tiles_m = (M + 2 * kPairBM - 1) / (2 * kPairBM);
+    const int tiles_n = (N + kPairBN - 1) / kPairBN;
+    const int tiles = tiles_m * tiles_n;
+    const int max_pairs = dev->sm_count / 2;
+    const int pairs = tiles < max_pairs ? tiles : max_pairs;
+    gemm_pair_kernel<<<2 * pairs, kPairThreads, kPairSmem, stream>>>(ta, tb, C, M, N, K, ldc, tiles_m, tiles_n,
+                                                                    dev->status_word);
+    TCB_CUDA(cudaGetLastError());
+    return TC_OK;
+}
+
+}  // namespace tcb
