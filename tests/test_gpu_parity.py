@@ -30,6 +30,7 @@ def assert_close(out, ref, max_abs=oracle.MAX_ABS_TOL, rel_fro=oracle.REL_FRO_TO
         (1, 8, 8), (129, 257, 72), (200, 300, 136), (1000, 24, 4104),  # ragged edges, K tail, many k-blocks
         (1024, 1024, 1024),                      # configuration C1
         (1024, 1024, 2048), (2048, 2048, 2048),
+        (2304, 2304, 64), (2250, 2300, 136), (4100, 2310, 328),  # enough 256x256 tiles for the CTA-pair kernel, ragged edges
     ],
 )
 def test_gemm_matches_oracle(cuda_ops, clean_status, m, n, k):
