@@ -340,13 +340,16 @@ class LstmWorkload(Workload):
         self.c0 = torch.zeros(self.batch, self.hidden, device=device)
         self.h_all = torch.empty(self.steps, self.batch, self.hidden, dtype=torch.float16, device=device)
         self.c_t = torch.empty(self.batch, self.hidden, device=device)
+        if device.type == "cuda":
+            from tiledcuda_b200 import ops
+            self.ws = torch.empty(ops.lstm_chain_workspace_bytes(self.steps, self.batch, self.hidden) // 4, device=device)
 
     def step(self):
         from tiledcuda_b200 import ops
-        ops.lstm_chain(self.w, self.u, None, self.x, self.h0, self.c0, self.h_all, self.c_t)
+        ops.lstm_chain(self.w, self.u, None, self.x, self.h0, self.c0, self.h_all, self.c_t, workspace=self.ws)
 
     def launches_per_step(self):
-        return self.steps
+        return self.steps + 1  # one GEMM for the input projections of all steps, then one launch per step
 
     def cpu_sample(self):
         from oracle import oracle

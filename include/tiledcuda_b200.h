@@ -88,6 +88,16 @@ int tc_lstm_chain_f16(const void* W, const void* U, const float* bias, const voi
                       const float* c0, void* h_all, float* c_out, int64_t steps, int64_t batch, int64_t input,
                       int64_t hidden, tc_stream_t stream);
 
+/* The same chain with caller-provided scratch memory: the input projections x_t W^T of all steps are
+ * computed first as one large GEMM into `workspace` (fp32 [steps, batch, 4*hidden], 16-byte aligned,
+ * tc_lstm_chain_workspace_bytes() bytes) and each step only runs the recurrent product h U^T. Same
+ * results as tc_lstm_chain_f16 up to fp32 summation order. No counterpart in the reference
+ * (Makefile:3 only names test_lstm_cell). */
+int64_t tc_lstm_chain_workspace_bytes(int64_t steps, int64_t batch, int64_t hidden);
+int tc_lstm_chain_ws_f16(const void* W, const void* U, const float* bias, const void* x, const void* h0,
+                         const float* c0, void* h_all, float* c_out, int64_t steps, int64_t batch, int64_t input,
+                         int64_t hidden, void* workspace, int64_t workspace_bytes, tc_stream_t stream);
+
 /* ScatterND assignment: for each of the n index tuples t (k integers each, int64 when idx_is_int64
  * else int32), data[idx[t,0], ..., idx[t,k-1], :] = updates[t, :], where data has `rank` dimensions
  * `dims` (row-major, elements of elem_bytes bytes) and the slice is the product of dims[k..rank).

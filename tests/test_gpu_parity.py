@@ -225,6 +225,29 @@ def test_lstm_chain_configuration_c4(cuda_ops, clean_status):
         h_prev, c_prev = h1, c1
 
 
+@pytest.mark.parametrize("steps,batch,inp,hidden,bias", [(5, 100, 72, 48, True), (64, 256, 1024, 1024, False)])
+def test_lstm_chain_with_workspace_matches_oracle_and_plain_chain(cuda_ops, clean_status, steps, batch, inp, hidden, bias):
+    """The chain that hoists x W^T of all steps into one GEMM (caller-provided scratch) against the oracle and
+    against the chain without scratch."""
+    w, u, b, x, h0, c0 = oracle.lstm_inputs(steps, batch, inp, hidden, with_bias=bias)
+    dev = [t.to(DEV) if t is not None else None for t in (w, u, b, x, h0, c0)]
+    h_ws = torch.empty(steps, batch, hidden, dtype=torch.float16, device=DEV)
+    c_ws = torch.empty(batch, hidden, device=DEV)
+    nbytes = cuda_ops.lstm_chain_workspace_bytes(steps, batch, hidden)
+    assert nbytes == steps * batch * 4 * hidden * 4
+    ws = torch.empty(nbytes // 4, device=DEV)
+    cuda_ops.lstm_chain(*dev, h_ws, c_ws, workspace=ws)
+    rh, rc = oracle.lstm_chain(w, u, b, x, h0, c0)
+    assert_close(h_ws, rh)
+    assert_close(c_ws, rc)
+    h_plain = torch.empty_like(h_ws)
+    c_plain = torch.empty_like(c_ws)
+    cuda_ops.lstm_chain(*dev, h_plain, c_plain)
+    assert_close(h_ws, h_plain, max_abs=2e-3, rel_fro=2e-4)
+    with pytest.raises(Exception, match="workspace"):
+        cuda_ops.lstm_chain(*dev, h_ws, c_ws, workspace=ws[: ws.numel() // 2])
+
+
 # ------------------------------------------------------------------------------------- scatter_nd
 def test_scatter_nd_reference_test_case(cuda_ops, clean_status, golden_dir):
     """tests/python/test_scatter_nd.py:22-54: data [7,8,9,10] fp32, five (i, j) pairs, 90-element slices."""

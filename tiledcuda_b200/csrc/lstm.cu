@@ -33,6 +33,7 @@ struct LstmCfg {
 };
 
 struct LstmParams {
+    const float* gx;      // [B, 4H] fp32 pre-activations x W^T computed beforehand, or null
     const float* bias;    // [4H] or null
     const float* c_prev;  // [B, H]
     float* c_out;         // [B, H]
@@ -66,7 +67,7 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     const int lane = threadIdx.x & 31;
     const int j0 = blockIdx.x * HT;        // first hidden unit of this CTA
     const int b0 = blockIdx.y * kLstmBM;   // first batch row
-    const int kb_x = (p.input + kLstmBK - 1) / kLstmBK;
+    const int kb_x = p.gx != nullptr ? 0 : (p.input + kLstmBK - 1) / kLstmBK;
     const int kb_h = (p.hidden + kLstmBK - 1) / kLstmBK;
     const int k_blocks = kb_x + kb_h;
 
@@ -87,6 +88,7 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    grid_launch_dependents();  // the next step's CTAs may start their own set-up as SMs free up
 
     if (warp == 0) {
         if (lane == 0) {
@@ -96,18 +98,22 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             tma_prefetch_desc(&tmap_u);
             int stage = 0;
             uint32_t phase = 0;
+            // h_prev (and c_prev, read by the epilogue) come from the previous launch in the stream: with
+            // programmatic dependent launch everything above overlapped its tail, the data is awaited here.
+            grid_dependency_wait();
             for (int kb = 0; kb < k_blocks; ++kb) {
                 if (!mbar_wait(&bar_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) break;
+                // Every CTA of a batch tile reads the same x / h tiles: each starts at a different K block
+                // and wraps around, so that at any moment the CTAs pull different lines out of L2.
                 const bool from_x = kb < kb_x;
                 const CUtensorMap* ta = from_x ? &tmap_x : &tmap_h;
                 const CUtensorMap* tb = from_x ? &tmap_w : &tmap_u;
-                const int kcoord = (from_x ? kb : kb - kb_x) * kLstmBK;
+                const int part = from_x ? kb_x : kb_h;
+                const int kcoord = ((from_x ? kb : kb - kb_x) + static_cast<int>(blockIdx.x)) % part * kLstmBK;
                 mbar_arrive_expect_tx(&bar_full[stage], Cfg::kStageBytes);
                 tma_load_2d(smem_a + stage * Cfg::kABytes, ta, &bar_full[stage], kcoord, b0);
-#pragma unroll
-                for (int g = 0; g < 4; ++g)
-                    tma_load_2d(smem_b + stage * Cfg::kBBytes + g * Cfg::kGateBytes, tb, &bar_full[stage], kcoord,
-                                g * p.hidden + j0);
+                // one 3-D box {64 k, HT units, 4 gates}: the four gate slabs land side by side, gate-major
+                tma_load_3d(smem_b + stage * Cfg::kBBytes, tb, &bar_full[stage], kcoord, j0, 0);
                 if (++stage == Cfg::kStages) {
                     stage = 0;
                     phase ^= 1u;
@@ -145,6 +151,18 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     } else {
         const int quarter = warp & 3;
         const int row = b0 + quarter * 32 + lane;
+        // The hoisted input projections do not depend on the previous step: fetch the first 16 units of the
+        // four gates into registers before waiting for anything.
+        float4 pre[16];
+        const bool has_pre = p.gx != nullptr && row < p.batch && j0 < p.hidden;
+        if (has_pre) {
+            const float* g = p.gx + static_cast<int64_t>(row) * (4 * p.hidden) + j0;
+#pragma unroll
+            for (int gate = 0; gate < 4; ++gate)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) pre[gate * 4 + q] = __ldg(reinterpret_cast<const float4*>(g + gate * p.hidden) + q);
+        }
+        grid_dependency_wait();
         if (mbar_wait_warp(bar_acc_full, 0, abort_word, kDevTimeoutEpilogue)) {
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -178,6 +196,20 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                         float xf = __uint_as_float(gf[i]);
                         float xg = __uint_as_float(gg[i]);
                         float xo = __uint_as_float(go[i]);
+                        if (p.gx != nullptr) {
+                            if (u0 == 0) {
+                                xi += reinterpret_cast<const float*>(&pre[0])[i];
+                                xf += reinterpret_cast<const float*>(&pre[4])[i];
+                                xg += reinterpret_cast<const float*>(&pre[8])[i];
+                                xo += reinterpret_cast<const float*>(&pre[12])[i];
+                            } else {
+                                const float* g = p.gx + static_cast<int64_t>(row) * (4 * p.hidden) + unit0 + i;
+                                xi += __ldg(g);
+                                xf += __ldg(g + p.hidden);
+                                xg += __ldg(g + 2 * p.hidden);
+                                xo += __ldg(g + 3 * p.hidden);
+                            }
+                        }
                         if (p.bias != nullptr) {
                             xi += __ldg(p.bias + 0 * p.hidden + unit0 + i);
                             xf += __ldg(p.bias + 1 * p.hidden + unit0 + i);
@@ -228,11 +260,21 @@ static int pick_ht(const DeviceInfo* dev, int64_t batch, int64_t hidden) {
     return ctas16 <= 2 * dev->sm_count ? 16 : 32;
 }
 
+// A [4*hidden, cols] weight matrix seen as [4 gates, hidden, cols]; one box covers 64 columns of HT units of
+// all four gates, so a stage's whole B operand is a single TMA operation (TMA is limited by operations
+// per second as much as by bytes: four 2 KiB boxes per stage cost more than the 16 KiB A tile).
+static int encode_gates(CUtensorMap* out, const void* base, int64_t hidden, int64_t cols, uint32_t ht) {
+    const uint64_t dims[3] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(hidden), 4};
+    const uint64_t strides[2] = {static_cast<uint64_t>(cols) * 2, static_cast<uint64_t>(hidden) * static_cast<uint64_t>(cols) * 2};
+    const uint32_t box[3] = {kLstmBK, ht, 4};
+    return encode_tmap_f16_sw128(out, base, 3, dims, strides, box);
+}
+
 static int encode_weights(LstmWeights* lw, const DeviceInfo* dev, const void* W, const void* U, int64_t batch,
                           int64_t input, int64_t hidden) {
     lw->ht = pick_ht(dev, batch, hidden);
-    if (int rc = encode_2d(&lw->w, W, 4 * hidden, input, static_cast<uint32_t>(lw->ht))) return rc;
-    return encode_2d(&lw->u, U, 4 * hidden, hidden, static_cast<uint32_t>(lw->ht));
+    if (int rc = encode_gates(&lw->w, W, hidden, input, static_cast<uint32_t>(lw->ht))) return rc;
+    return encode_gates(&lw->u, U, hidden, hidden, static_cast<uint32_t>(lw->ht));
 }
 
 template <int HT>
@@ -246,18 +288,28 @@ static int launch_lstm(const CUtensorMap& tx, const LstmWeights& lw, const CUten
         configured[dev->device] = true;
     }
     const dim3 grid(static_cast<unsigned>((p.hidden + HT - 1) / HT), static_cast<unsigned>((p.batch + kLstmBM - 1) / kLstmBM));
-    kernel<<<grid, kLstmThreads, Cfg::kSmem, stream>>>(tx, lw.w, th, lw.u, p);
-    TCB_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kLstmThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    TCB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tx, lw.w, th, lw.u, p));
     return TC_OK;
 }
 
-static int lstm_step(const LstmWeights& lw, const float* bias, const void* x, const void* h_prev, const float* c_prev,
-                     void* h_out, float* c_out, int64_t batch, int64_t input, int64_t hidden, const DeviceInfo* dev,
-                     cudaStream_t stream) {
+static int lstm_step(const LstmWeights& lw, const float* gx, const float* bias, const void* x, const void* h_prev,
+                     const float* c_prev, void* h_out, float* c_out, int64_t batch, int64_t input, int64_t hidden,
+                     const DeviceInfo* dev, cudaStream_t stream) {
     CUtensorMap tx, th;
     if (int rc = encode_2d(&tx, x, batch, input, kLstmBM)) return rc;
     if (int rc = encode_2d(&th, h_prev, batch, hidden, kLstmBM)) return rc;
     LstmParams p;
+    p.gx = gx;
     p.bias = bias;
     p.c_prev = c_prev;
     p.c_out = c_out;
@@ -294,12 +346,13 @@ extern "C" int tc_lstm_cell_f16(const void* W, const void* U, const float* bias,
     if (int rc = current_device(&dev)) return rc;
     LstmWeights lw;
     if (int rc = encode_weights(&lw, dev, W, U, batch, input, hidden)) return rc;
-    return lstm_step(lw, bias, x, h_prev, c_prev, h_out, c_out, batch, input, hidden, dev, static_cast<cudaStream_t>(stream));
+    return lstm_step(lw, nullptr, bias, x, h_prev, c_prev, h_out, c_out, batch, input, hidden, dev,
+                     static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int tc_lstm_chain_f16(const void* W, const void* U, const float* bias, const void* x, const void* h0,
-                                 const float* c0, void* h_all, float* c_out, int64_t steps, int64_t batch,
-                                 int64_t input, int64_t hidden, tc_stream_t stream) {
+static int lstm_chain_impl(const void* W, const void* U, const float* bias, const void* x, const void* h0, const float* c0,
+                           void* h_all, float* c_out, int64_t steps, int64_t batch, int64_t input, int64_t hidden,
+                           float* workspace, cudaStream_t st) {
     using namespace tcb;
     TCB_REQUIRE(steps > 0, "lstm_chain: steps must be positive");
     if (int rc = check_lstm("lstm_chain", W, U, x, h0, c0, h_all, c_out, batch, input, hidden)) return rc;
@@ -308,15 +361,46 @@ extern "C" int tc_lstm_chain_f16(const void* W, const void* U, const float* bias
     if (int rc = current_device(&dev)) return rc;
     LstmWeights lw;
     if (int rc = encode_weights(&lw, dev, W, U, batch, input, hidden)) return rc;
-    auto* st = static_cast<cudaStream_t>(stream);
+    if (workspace != nullptr) {
+        // The input projections do not depend on the recurrence: x W^T for all steps is one large GEMM
+        // ([steps*batch, input] x [input, 4*hidden], fp32 result) and each step adds its slab in the epilogue.
+        if (int rc = tc_gemm_f16_f32(x, W, workspace, steps * batch, 4 * hidden, input, input, input, 4 * hidden, st)) return rc;
+    }
     const __half* xs = static_cast<const __half*>(x);
     __half* hs = static_cast<__half*>(h_all);
     for (int64_t t = 0; t < steps; ++t) {
         const void* h_prev = t == 0 ? h0 : static_cast<const void*>(hs + (t - 1) * batch * hidden);
         const float* c_prev = t == 0 ? c0 : c_out;
-        if (int rc = lstm_step(lw, bias, xs + t * batch * input, h_prev, c_prev, hs + t * batch * hidden, c_out, batch,
+        const float* gx = workspace != nullptr ? workspace + t * batch * 4 * hidden : nullptr;
+        if (int rc = lstm_step(lw, gx, bias, xs + t * batch * input, h_prev, c_prev, hs + t * batch * hidden, c_out, batch,
                                input, hidden, dev, st))
             return rc;
     }
     return TC_OK;
+}
+
+extern "C" int tc_lstm_chain_f16(const void* W, const void* U, const float* bias, const void* x, const void* h0,
+                                 const float* c0, void* h_all, float* c_out, int64_t steps, int64_t batch,
+                                 int64_t input, int64_t hidden, tc_stream_t stream) {
+    return lstm_chain_impl(W, U, bias, x, h0, c0, h_all, c_out, steps, batch, input, hidden, nullptr,
+                           static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int64_t tc_lstm_chain_workspace_bytes(int64_t steps, int64_t batch, int64_t hidden) {
+    if (steps <= 0 || batch <= 0 || hidden <= 0) return 0;
+    return steps * batch * 4 * hidden * static_cast<int64_t>(sizeof(float));
+}
+
+extern "C" int tc_lstm_chain_ws_f16(const void* W, const void* U, const float* bias, const void* x, const void* h0,
+                                    const float* c0, void* h_all, float* c_out, int64_t steps, int64_t batch,
+                                    int64_t input, int64_t hidden, void* workspace, int64_t workspace_bytes,
+                                    tc_stream_t stream) {
+    using namespace tcb;
+    TCB_REQUIRE(workspace != nullptr, "lstm_chain_ws: workspace is NULL");
+    TCB_REQUIRE(workspace_bytes >= tc_lstm_chain_workspace_bytes(steps, batch, hidden),
+                "lstm_chain_ws: workspace holds %lld bytes, %lld needed", (long long)workspace_bytes,
+                (long long)tc_lstm_chain_workspace_bytes(steps, batch, hidden));
+    TCB_REQUIRE(aligned16(workspace), "lstm_chain_ws: workspace must be 16-byte aligned");
+    return lstm_chain_impl(W, U, bias, x, h0, c0, h_all, c_out, steps, batch, input, hidden, static_cast<float*>(workspace),
+                           static_cast<cudaStream_t>(stream));
 }

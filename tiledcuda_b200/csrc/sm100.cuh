@@ -38,6 +38,13 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// wait: blocks until the grids this launch depends on have completed and their writes are visible (a no-op
+// when the launch carries no programmatic dependency). launch_dependents: lets the next launch in the stream
+// begin its own prologue while this grid is still running.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- mbarrier ------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");

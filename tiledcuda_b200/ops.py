@@ -194,8 +194,13 @@ def lstm_chain(
     c0: torch.Tensor,
     h_all: torch.Tensor,
     c_out: torch.Tensor,
+    workspace: torch.Tensor | None = None,
 ) -> None:
-    """`steps` chained cells: x fp16 [T, B, I]; h_all fp16 [T, B, H] gets every h_t; c_out fp32 [B, H] gets c_T."""
+    """`steps` chained cells: x fp16 [T, B, I]; h_all fp16 [T, B, H] gets every h_t; c_out fp32 [B, H] gets c_T.
+
+    With `workspace` (a CUDA tensor of at least lstm_chain_workspace_bytes(T, B, H) bytes) the input
+    projections of all steps are computed first as one GEMM and each step only runs h @ U.T.
+    """
     _need(w, "w", torch.float16)
     _need(u, "u", torch.float16)
     _need(x, "x", torch.float16)
@@ -215,11 +220,26 @@ def lstm_chain(
         raise ValueError("c0 and c_out must be [batch, hidden]")
     lib = _lib.load()
     with torch.cuda.device(x.device):
-        _lib.check(
-            "tc_lstm_chain_f16",
-            lib.tc_lstm_chain_f16(_ptr(w), _ptr(u), _ptr(bias), _ptr(x), _ptr(h0), _ptr(c0), _ptr(h_all), _ptr(c_out),
-                                  steps, batch, inp, hidden, _stream()),
-        )
+        if workspace is None:
+            _lib.check(
+                "tc_lstm_chain_f16",
+                lib.tc_lstm_chain_f16(_ptr(w), _ptr(u), _ptr(bias), _ptr(x), _ptr(h0), _ptr(c0), _ptr(h_all), _ptr(c_out),
+                                      steps, batch, inp, hidden, _stream()),
+            )
+        else:
+            if not workspace.is_cuda or not workspace.is_contiguous():
+                raise ValueError("workspace must be a contiguous CUDA tensor")
+            _lib.check(
+                "tc_lstm_chain_ws_f16",
+                lib.tc_lstm_chain_ws_f16(_ptr(w), _ptr(u), _ptr(bias), _ptr(x), _ptr(h0), _ptr(c0), _ptr(h_all), _ptr(c_out),
+                                         steps, batch, inp, hidden, _ptr(workspace), workspace.numel() * workspace.element_size(),
+                                         _stream()),
+            )
+
+
+def lstm_chain_workspace_bytes(steps: int, batch: int, hidden: int) -> int:
+    """Bytes of scratch memory lstm_chain needs to hoist the input projections out of the recurrence."""
+    return int(_lib.load().tc_lstm_chain_workspace_bytes(steps, batch, hidden))
 
 
 def scatter_nd(data: torch.Tensor, indices: torch.Tensor, updates: torch.Tensor) -> None:
