@@ -98,6 +98,22 @@ int tc_lstm_chain_ws_f16(const void* W, const void* U, const float* bias, const 
                          const float* c0, void* h_all, float* c_out, int64_t steps, int64_t batch, int64_t input,
                          int64_t hidden, void* workspace, int64_t workspace_bytes, tc_stream_t stream);
 
+/* The chain of tc_lstm_chain_ws_f16 for callers that cannot allocate device memory or hand over scratch:
+ * code running under a stream capture, loops whose memory was budgeted at start-up, plug-ins that only
+ * receive input and output buffers. It calls no cudaMalloc / cudaFree and no allocating library routine.
+ * Its scratch (fp32 [steps, batch, 4*hidden]) is a 64 MiB array that is part of the library image, so
+ * steps * batch * 4 * hidden * 4 must not exceed 67,108,864 bytes (TC_ERR_UNSUPPORTED otherwise), and
+ * every GPU that loads the library holds those 64 MiB until the library is unloaded. All calls on one
+ * device share that array: calls whose kernels overlap on the GPU (different streams, or the same
+ * stream from two threads) race on it; run them one after the other. The first call on a device looks
+ * up the array's device address; make that first call before any stream capture begins. A call with
+ * steps == 0 launches nothing: it synchronises the device and returns TC_ERR_DEVICE if a kernel of an
+ * earlier call of this entry point recorded a timeout (tc_device_status() does not cover this path).
+ * Arguments otherwise as tc_lstm_chain_f16. It has no counterpart in the reference. */
+int tc_lstm_chain_static_f16(const void* W, const void* U, const float* bias, const void* x, const void* h0,
+                             const float* c0, void* h_all, float* c_out, int64_t steps, int64_t batch, int64_t input,
+                             int64_t hidden, tc_stream_t stream);
+
 /* ScatterND assignment: for each of the n index tuples t (k integers each, int64 when idx_is_int64
  * else int32), data[idx[t,0], ..., idx[t,k-1], :] = updates[t, :], where data has `rank` dimensions
  * `dims` (row-major, elements of elem_bytes bytes) and the slice is the product of dims[k..rank).

@@ -36,6 +36,10 @@ SIGNATURES = {
         ctypes.c_int,
         [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_vp, c_i64, c_vp],
     ),
+    "tc_lstm_chain_static_f16": (
+        ctypes.c_int,
+        [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_vp],
+    ),
     "tc_scatter_nd": (
         ctypes.c_int,
         [c_vp, c_vp, c_vp, ctypes.c_int, ctypes.POINTER(c_i64), ctypes.c_int, c_i64, ctypes.c_int, ctypes.c_int, c_vp],

@@ -233,6 +233,34 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, float* C, i
 int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int M, int N, int K, int64_t ldc,
                      const DeviceInfo* dev, cudaStream_t stream);
 
+// The dispatch of tc_gemm_f16_f32 for a caller that brings its own device record (and therefore its own
+// status word) instead of the lazily allocated per-device one. Arguments are trusted: the caller has
+// validated them. Used by entry points that must not allocate.
+int gemm_f16_f32_on(const DeviceInfo* dev, const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K,
+                    int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t stream) {
+    const int64_t tiles_pair = ((M + 255) / 256) * ((N + 255) / 256);
+    const bool use_pair = tiles_pair >= dev->sm_count / 2;
+    const int64_t tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
+    const bool use128 = !use_pair && ((N <= 128) || (tiles256 < dev->sm_count));
+    const uint32_t bn = (use128 || use_pair) ? 128u : 256u;
+    CUtensorMap ta, tb;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(lda) * 2};
+        const uint32_t box[2] = {kGemmBK, kGemmBM};
+        if (int rc = encode_tmap_f16_sw128(&ta, A, 2, dims, strides, box)) return rc;
+    }
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(ldb) * 2};
+        const uint32_t box[2] = {kGemmBK, bn};
+        if (int rc = encode_tmap_f16_sw128(&tb, B, 2, dims, strides, box)) return rc;
+    }
+    if (use_pair) return launch_gemm_pair(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream);
+    if (use128) return launch_gemm<128, 6>(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream);
+    return launch_gemm<256, 4>(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream);
+}
+
 }  // namespace tcb
 
 extern "C" int tc_gemm_f16_f32(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,

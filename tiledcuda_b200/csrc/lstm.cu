@@ -11,10 +11,16 @@
 //
 // The reference snapshot only names this op (Makefile:3 `test_lstm_cell`); the math is that of
 // torch.nn.LSTMCell with gate order (i, f, g, o).
+#include <mutex>
+
 #include "host.h"
 #include "sm100.cuh"
 
 namespace tcb {
+
+// GEMM dispatch for a caller-supplied device record (gemm.cu).
+int gemm_f16_f32_on(const DeviceInfo* dev, const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K,
+                    int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t stream);
 
 constexpr int kLstmBM = 128;
 constexpr int kLstmBK = 64;
@@ -403,4 +409,112 @@ extern "C" int tc_lstm_chain_ws_f16(const void* W, const void* U, const float* b
     TCB_REQUIRE(aligned16(workspace), "lstm_chain_ws: workspace must be 16-byte aligned");
     return lstm_chain_impl(W, U, bias, x, h0, c0, h_all, c_out, steps, batch, input, hidden, static_cast<float*>(workspace),
                            static_cast<cudaStream_t>(stream));
+}
+
+namespace tcb {
+
+// ---------------------------------------------------------------------------------------------------
+// The chain for callers that may not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they run the chain: a caller
+// inside a stream capture (allocation is illegal there), a real-time or serving loop whose memory
+// budget was fixed at start-up, or a plug-in that was handed buffers for inputs and outputs only and has
+// no allocator of its own. tc_lstm_chain_ws_f16 asks them for scratch memory they cannot provide, and every
+// other entry point may allocate the per-device status word on its first use. This variant needs neither:
+// its scratch (the hoisted input projections) and its status word live in the arrays below, which are part
+// of the library image. Every GPU that loads the library therefore holds kStaticScratchBytes (+ 16) bytes
+// for as long as the library is loaded, whether or not this entry point is ever called.
+// ---------------------------------------------------------------------------------------------------
+constexpr int64_t kStaticScratchFloats = 16ll * 1024 * 1024;                 // 64 MiB
+constexpr int64_t kStaticScratchBytes = kStaticScratchFloats * sizeof(float);
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+static __device__ __align__(256) uint32_t g_static_status[4];
+
+struct StaticDevice {
+    bool ready = false;
+    DeviceInfo info;          // status_word points at this device's copy of g_static_status
+    float* scratch = nullptr;  // this device's copy of g_static_scratch
+};
+static StaticDevice g_static_dev[64];
+static std::mutex g_static_mu;
+
+// Set-up, once per device, with that device current. In host code `g_static_scratch` is only a handle for
+// the runtime, not a device address, so the address each device gave its copy is asked for here and that
+// is what the kernels receive. Nothing is allocated: cudaGetSymbolAddress and the attribute queries only
+// look things up.
+static int static_device(const StaticDevice** out) {
+    int dev = -1;
+    TCB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(TC_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    StaticDevice& sd = g_static_dev[dev];
+    if (!sd.ready) {
+        DeviceInfo d;
+        d.device = dev;
+        TCB_CUDA(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+        TCB_CUDA(cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, dev));
+        TCB_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        TCB_CUDA(cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        if (d.cc_major != 10)
+            return fail(TC_ERR_UNSUPPORTED, "device %d is sm_%d%d; these kernels are built for sm_100a only", dev, d.cc_major,
+                        d.cc_minor);
+        void* scratch = nullptr;
+        void* status = nullptr;
+        TCB_CUDA(cudaGetSymbolAddress(&scratch, g_static_scratch));
+        TCB_CUDA(cudaGetSymbolAddress(&status, g_static_status));
+        d.status_word = static_cast<uint32_t*>(status);
+        sd.info = d;
+        sd.scratch = static_cast<float*>(scratch);
+        sd.ready = true;
+    }
+    *out = &sd;
+    return TC_OK;
+}
+
+}  // namespace tcb
+
+extern "C" int tc_lstm_chain_static_f16(const void* W, const void* U, const float* bias, const void* x, const void* h0,
+                                        const float* c0, void* h_all, float* c_out, int64_t steps, int64_t batch,
+                                        int64_t input, int64_t hidden, tc_stream_t stream) {
+    using namespace tcb;
+    const StaticDevice* sd = nullptr;
+    if (int rc = static_device(&sd)) return rc;
+    auto* st = static_cast<cudaStream_t>(stream);
+    if (steps == 0) {
+        // Status query for this path: its kernels record timeouts in the library's own status word, which
+        // tc_device_status() does not see. Synchronises the device; launches nothing.
+        uint32_t word = 0;
+        TCB_CUDA(cudaDeviceSynchronize());
+        TCB_CUDA(cudaMemcpy(&word, sd->info.status_word, sizeof(word), cudaMemcpyDeviceToHost));
+        if (word != 0) {
+            TCB_CUDA(cudaMemset(sd->info.status_word, 0, 4 * sizeof(uint32_t)));
+            return fail(TC_ERR_DEVICE, "lstm_chain_static: a kernel of an earlier call recorded status %u", word);
+        }
+        return TC_OK;
+    }
+    TCB_REQUIRE(steps > 0, "lstm_chain_static: steps must not be negative");
+    if (int rc = check_lstm("lstm_chain_static", W, U, x, h0, c0, h_all, c_out, batch, input, hidden)) return rc;
+    TCB_REQUIRE((batch * input) % 8 == 0 && (batch * hidden) % 8 == 0,
+                "lstm_chain_static: per-step slabs must stay 16-byte aligned");
+    const int64_t need = steps * batch * 4 * hidden * static_cast<int64_t>(sizeof(float));
+    if (need > kStaticScratchBytes)
+        return fail(TC_ERR_UNSUPPORTED,
+                    "lstm_chain_static: steps * batch * 4 * hidden * 4 = %lld bytes of scratch exceed the %lld bytes built into "
+                    "the library; use tc_lstm_chain_ws_f16 with your own workspace or tc_lstm_chain_f16",
+                    (long long)need, (long long)kStaticScratchBytes);
+    const DeviceInfo* dev = &sd->info;
+    LstmWeights lw;
+    if (int rc = encode_weights(&lw, dev, W, U, batch, input, hidden)) return rc;
+    // The GEMM overwrites every float of the scratch region the steps read, so nothing has to be cleared.
+    if (int rc = gemm_f16_f32_on(dev, x, W, sd->scratch, steps * batch, 4 * hidden, input, input, input, 4 * hidden, st)) return rc;
+    const __half* xs = static_cast<const __half*>(x);
+    __half* hs = static_cast<__half*>(h_all);
+    for (int64_t t = 0; t < steps; ++t) {
+        const void* h_prev = t == 0 ? h0 : static_cast<const void*>(hs + (t - 1) * batch * hidden);
+        const float* c_prev = t == 0 ? c0 : c_out;
+        if (int rc = lstm_step(lw, sd->scratch + t * batch * 4 * hidden, bias, xs + t * batch * input, h_prev, c_prev,
+                               hs + t * batch * hidden, c_out, batch, input, hidden, dev, st))
+            return rc;
+    }
+    return TC_OK;
 }
