@@ -1,0 +1,300 @@
+// Test kernels written against the tile API headers (tiledcuda_b200/include), the way a user of the
+// library writes kernels: declare tile types, iterate, load, multiply, store. Each kernel is one CTA of
+// 128 threads, like the single-CTA kernels of the reference's unit tests (tests/cpp/cell/test_gemm.cu,
+// test_g2s_load.cu, test_swizzled_copy.cu, test_softmax.cu, test_reduce.cu, test_broadcast.cu), whose
+// shapes the Python tests replay. Results are copied back and compared on the host: nothing here asserts
+// or traps on the device. A kernel that gives up on a bounded wait writes 1 to *status.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "cell/mod.hpp"
+#include "types/mod.hpp"
+
+using namespace tiledcuda::cell;
+namespace tl = tiledcuda::cell::tile_layout;
+using WarpLayout = tl::RowMajor<4, 1>;
+
+__device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
+    const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    return p + ((1024u - (a & 1023u)) & 1023u);
+}
+
+// ------------------------------------------------------------------------------------ copy round trip
+// global -> shared (operand or plain layout) -> global; must reproduce the input exactly.
+template <typename T, typename GLayout, bool kSwizzled>
+__global__ void k_roundtrip(const T* in, T* out) {
+    extern __shared__ uint8_t raw[];
+    using Global = GlobalTile<T, GLayout>;
+    using Shared = SharedTile<T, GLayout, kSwizzled>;
+    Shared s(reinterpret_cast<T*>(align1024(raw)));
+    Global gin(in), gout(out);
+    copy::GlobalToSharedLoader<Shared, WarpLayout> load;
+    copy::SharedToGlobalStorer<Shared, WarpLayout> store;
+    load(gin, s);
+    __copy_async();
+    __syncthreads();
+    store(s, gout);
+}
+
+// ------------------------------------------------------------------------------------ tile GEMM
+// C[M,N] = A[M,K] B[K,N] with A row-major, B column-major, fp32 C, K walked in chunks of TK.
+template <int M, int N, int K, int TK, bool kSwizzled>
+__global__ void k_tile_gemm(const __half* dA, const __half* dB, float* dC, int* status) {
+    extern __shared__ uint8_t raw[];
+    using GlobalA = GlobalTile<__half, tl::RowMajor<M, K>>;
+    using GlobalB = GlobalTile<__half, tl::ColMajor<K, N>>;
+    using GlobalC = GlobalTile<float, tl::RowMajor<M, N>>;
+    using IterA = GTileIterator<GlobalA, TileShape<M, TK>>;
+    using IterB = GTileIterator<GlobalB, TileShape<TK, N>>;
+    using SharedA = SharedTile<__half, tl::RowMajor<M, TK>, kSwizzled>;
+    using SharedB = SharedTile<__half, tl::ColMajor<TK, N>, kSwizzled>;
+    using Acc = TmemTile<float, tl::RowMajor<128, N>>;
+    using RegC = RowFragment<float, N>;
+
+    uint8_t* smem = align1024(raw);
+    SharedA sA(reinterpret_cast<__half*>(smem));               // 64 KiB reserved: the MMA always reads 128 rows
+    SharedB sB(reinterpret_cast<__half*>(smem + 64 * 1024));   // up to 256 x 128 fp16 = 64 KiB
+    uint64_t* bar_mem = reinterpret_cast<uint64_t*>(smem + 128 * 1024);
+    uint32_t* slot = reinterpret_cast<uint32_t*>(bar_mem + 1);
+
+    MmaBarrier bar(bar_mem);
+    if (threadIdx.x == 0) bar.init();
+    if (threadIdx.x < 32) copy::TmemAllocator::alloc(slot, tmem_alloc_columns(N));
+    __syncthreads();
+    Acc acc(*slot);
+
+    IterA gAs(dA);
+    IterB gBs(dB);
+    copy::GlobalToSharedLoader<SharedA, WarpLayout> load_a;
+    copy::GlobalToSharedLoader<SharedB, WarpLayout> load_b;
+    bool ok = true;
+    for (int k = 0; k < IterA::sc1; ++k) {
+        load_a(gAs(k), sA);
+        load_b(gBs(k), sB);
+        __copy_async();
+        __syncthreads();
+        compute::gemm(sA, sB, acc, k > 0);
+        if (threadIdx.x == 0) bar.commit();
+        ok = bar.wait() && ok;  // operands may be overwritten and acc read after this
+    }
+    if (ok) {
+        RegC rC;
+        copy::TmemToRegLoader<Acc, RegC>{}(acc, rC);
+        GlobalC gC(dC);
+        copy::RegToGlobalStorer<GlobalC, RegC, WarpLayout>{}(rC, gC);
+    } else if (threadIdx.x == 0) {
+        *status = 1;
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x < 32) copy::TmemAllocator::free(acc.address(), tmem_alloc_columns(N));
+}
+
+// ------------------------------------------------------------------------------------ fused two GEMMs
+// E[M,P] = fp16(A[M,K] B[K,N]) D[N,P], the intermediate going TMEM -> registers -> fp16 -> shared operand tile
+// (the structure of the reference's KeFusedGemm, examples/cpp/02_fused_two_gemms/fused_gemm.hpp:152-180).
+template <int M, int N, int K, int P>
+__global__ void k_tile_b2b(const __half* dA, const __half* dB, const __half* dD, float* dE, int* status) {
+    extern __shared__ uint8_t raw[];
+    using GlobalA = GlobalTile<__half, tl::RowMajor<M, K>>;
+    using GlobalB = GlobalTile<__half, tl::ColMajor<K, N>>;
+    using GlobalD = GlobalTile<__half, tl::ColMajor<N, P>>;
+    using GlobalE = GlobalTile<float, tl::RowMajor<M, P>>;
+    using SharedA = SharedTile<__half, tl::RowMajor<M, K>, true>;
+    using SharedB = SharedTile<__half, tl::ColMajor<K, N>, true>;
+    using SharedD = SharedTile<__half, tl::ColMajor<N, P>, true>;
+    using SharedS = SharedTile<__half, tl::RowMajor<128, N>, true>;  // the intermediate as operand A of the second product
+    using AccS = TmemTile<float, tl::RowMajor<128, N>>;
+    using AccE = TmemTile<float, tl::RowMajor<128, P>>;
+
+    uint8_t* smem = align1024(raw);
+    SharedA sA(reinterpret_cast<__half*>(smem));
+    SharedB sB(reinterpret_cast<__half*>(smem + 32 * 1024));
+    SharedD sD(reinterpret_cast<__half*>(smem + 64 * 1024));
+    SharedS sS(reinterpret_cast<__half*>(smem + 96 * 1024));
+    uint64_t* bar_mem = reinterpret_cast<uint64_t*>(smem + 128 * 1024);
+    uint32_t* slot = reinterpret_cast<uint32_t*>(bar_mem + 1);
+
+    MmaBarrier bar(bar_mem);
+    if (threadIdx.x == 0) bar.init();
+    if (threadIdx.x < 32) copy::TmemAllocator::alloc(slot, tmem_alloc_columns(N + P));
+    __syncthreads();
+    AccS accS(*slot);
+    AccE accE(*slot + N);
+
+    GlobalA gA(dA);
+    GlobalB gB(dB);
+    GlobalD gD(dD);
+    copy::GlobalToSharedLoader<SharedA, WarpLayout>{}(gA, sA);
+    copy::GlobalToSharedLoader<SharedB, WarpLayout>{}(gB, sB);
+    copy::GlobalToSharedLoader<SharedD, WarpLayout>{}(gD, sD);
+    __copy_async();
+    __syncthreads();
+
+    compute::gemm(sA, sB, accS, false);
+    if (threadIdx.x == 0) bar.commit();
+    bool ok = bar.wait();
+
+    RowFragment<float, N> rS;
+    copy::TmemToRegLoader<AccS, RowFragment<float, N>>{}(accS, rS);
+    copy::RegToSharedStorer<RowFragment<float, N>, WarpLayout>{}(rS, sS);  // rounds to fp16, writes the swizzled operand layout
+    fence_async_proxy();
+    __syncthreads();
+
+    compute::gemm(sS, sD, accE, false);
+    if (threadIdx.x == 0) bar.commit();
+    ok = bar.wait() && ok;
+    if (ok) {
+        RowFragment<float, P> rE;
+        copy::TmemToRegLoader<AccE, RowFragment<float, P>>{}(accE, rE);
+        GlobalE gE(dE);
+        copy::RegToGlobalStorer<GlobalE, RowFragment<float, P>, WarpLayout>{}(rE, gE);
+    } else if (threadIdx.x == 0) {
+        *status = 1;
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x < 32) copy::TmemAllocator::free(accS.address(), tmem_alloc_columns(N + P));
+}
+
+// ------------------------------------------------------------------------------------ row operations
+// in [128, C] fp32 -> softmax rows, row max, row sum, (x - max) broadcast, exp, per-warp column sums.
+template <int C>
+__global__ void k_row_ops(const float* in, float* softmax_out, float* row_max, float* row_sum, float* centered, float* col_sum) {
+    using Global = GlobalTile<float, tl::RowMajor<128, C>>;
+    using Reg = RowFragment<float, C>;
+    using Val = RowScalar<float>;
+    Global gin(in);
+    Reg x, y;
+    copy::GlobalToRegLoader<Reg, WarpLayout>{}(gin, x);
+    Val mx, sm;
+    compute::MaxReduce<Reg>{}(x, mx);
+    compute::SumReduce<Reg>{}(x, sm);
+    row_max[threadIdx.x] = mx(0, 0);
+    row_sum[threadIdx.x] = sm(0, 0);
+    compute::Softmax<Reg>{}(x, y);
+    Global gsoft(softmax_out);
+    copy::RegToGlobalStorer<Global, Reg, WarpLayout>{}(y, gsoft);
+    copy::copy(x, y);
+    compute::BroadcastSub<Val, Reg>{}(mx, y);
+    Global gcent(centered);
+    copy::RegToGlobalStorer<Global, Reg, WarpLayout>{}(y, gcent);
+    Reg cs;
+    compute::SumReduce<Reg, tl::Layout::kColMajor>{}(x, cs);   // sums over the 32 rows of this warp
+    if ((threadIdx.x & 31) == 0)
+        for (int j = 0; j < C; ++j) col_sum[(threadIdx.x >> 5) * C + j] = cs(0, j);
+}
+
+// ------------------------------------------------------------------------------------ C entry points
+template <typename Kernel>
+static int set_smem(Kernel k, int bytes) {
+    return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess ? 0 : -1;
+}
+
+#define GEMM_CASE(id, M, N, K, TK, SWZ)                                                   \
+    case id: {                                                                            \
+        auto kern = k_tile_gemm<M, N, K, TK, SWZ>;                                        \
+        if (set_smem(kern, 130 * 1024 + 1024)) return -3;                                 \
+        kern<<<1, 128, 130 * 1024 + 1024>>>(A, B, C, status);                             \
+        *m = M; *n = N; *k = K;                                                           \
+        break;                                                                            \
+    }
+
+// Shapes of the reference's test_gemm.cu:306-351 (M, N, K, chunk K), each with and without swizzle where the
+// chunk is a whole number of 64-element swizzle rows.
+extern "C" int tcx_gemm_case_count() { return 22; }
+extern "C" int tcx_tile_gemm(int id, const __half* A, const __half* B, float* C, int* status, int* m, int* n, int* k) {
+    switch (id) {
+        GEMM_CASE(0, 16, 16, 16, 16, false)
+        GEMM_CASE(1, 16, 16, 64, 64, true)
+        GEMM_CASE(2, 16, 32, 32, 32, false)
+        GEMM_CASE(3, 32, 32, 64, 64, true)
+        GEMM_CASE(4, 32, 64, 128, 64, true)
+        GEMM_CASE(5, 32, 64, 128, 64, false)
+        GEMM_CASE(6, 64, 64, 64, 64, true)
+        GEMM_CASE(7, 64, 64, 64, 32, false)
+        GEMM_CASE(8, 64, 128, 128, 128, true)
+        GEMM_CASE(9, 64, 32, 128, 128, false)
+        GEMM_CASE(10, 96, 48, 128, 64, true)
+        GEMM_CASE(11, 96, 48, 256, 64, false)
+        GEMM_CASE(12, 128, 128, 64, 64, true)
+        GEMM_CASE(13, 128, 128, 64, 64, false)
+        GEMM_CASE(14, 128, 128, 128, 32, false)
+        GEMM_CASE(15, 128, 128, 256, 128, true)
+        GEMM_CASE(16, 128, 64, 512, 64, true)
+        GEMM_CASE(17, 128, 256, 128, 64, true)
+        GEMM_CASE(18, 128, 256, 64, 16, false)
+        GEMM_CASE(19, 64, 256, 256, 128, true)
+        GEMM_CASE(20, 128, 80, 192, 64, true)
+        GEMM_CASE(21, 48, 112, 96, 16, false)
+        default: return -1;
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+#define RT_CASE(id, T, LAYOUT, R, C, SWZ)                                                 \
+    case id: {                                                                            \
+        auto kern = k_roundtrip<T, LAYOUT<R, C>, SWZ>;                                    \
+        if (set_smem(kern, 140 * 1024)) return -3;                                        \
+        kern<<<1, 128, 140 * 1024>>>(static_cast<const T*>(in), static_cast<T*>(out));    \
+        *rows = R; *cols = C; *elem = sizeof(T); *col_major = std::is_same_v<LAYOUT<R, C>, tl::ColMajor<R, C>>; \
+        break;                                                                            \
+    }
+
+extern "C" int tcx_roundtrip_case_count() { return 12; }
+extern "C" int tcx_roundtrip(int id, const void* in, void* out, int* rows, int* cols, int* elem, int* col_major) {
+    switch (id) {
+        RT_CASE(0, __half, tl::RowMajor, 16, 16, false)
+        RT_CASE(1, __half, tl::RowMajor, 16, 64, true)
+        RT_CASE(2, __half, tl::RowMajor, 64, 32, false)
+        RT_CASE(3, __half, tl::RowMajor, 64, 128, true)
+        RT_CASE(4, __half, tl::RowMajor, 128, 256, true)
+        RT_CASE(5, __half, tl::RowMajor, 128, 256, false)
+        RT_CASE(6, __half, tl::ColMajor, 64, 16, false)
+        RT_CASE(7, __half, tl::ColMajor, 128, 64, true)
+        RT_CASE(8, __half, tl::ColMajor, 64, 256, true)
+        RT_CASE(9, float, tl::RowMajor, 16, 16, false)
+        RT_CASE(10, float, tl::RowMajor, 64, 128, false)
+        RT_CASE(11, float, tl::ColMajor, 128, 32, false)
+        default: return -1;
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int tcx_tile_b2b(int id, const __half* A, const __half* B, const __half* D, float* E, int* status, int* m, int* n,
+                            int* k, int* p) {
+    const int smem = 130 * 1024 + 1024;
+    if (id == 0) {
+        auto kern = k_tile_b2b<64, 64, 64, 64>;
+        if (set_smem(kern, smem)) return -3;
+        kern<<<1, 128, smem>>>(A, B, D, E, status);
+        *m = 64; *n = 64; *k = 64; *p = 64;
+    } else if (id == 1) {
+        auto kern = k_tile_b2b<128, 128, 128, 128>;
+        if (set_smem(kern, smem)) return -3;
+        kern<<<1, 128, smem>>>(A, B, D, E, status);
+        *m = 128; *n = 128; *k = 128; *p = 128;
+    } else if (id == 2) {
+        auto kern = k_tile_b2b<32, 128, 64, 48>;
+        if (set_smem(kern, smem)) return -3;
+        kern<<<1, 128, smem>>>(A, B, D, E, status);
+        *m = 32; *n = 128; *k = 64; *p = 48;
+    } else {
+        return -1;
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int tcx_row_ops(int cols, const float* in, float* softmax_out, float* row_max, float* row_sum, float* centered,
+                           float* col_sum) {
+    if (cols == 16)
+        k_row_ops<16><<<1, 128>>>(in, softmax_out, row_max, row_sum, centered, col_sum);
+    else if (cols == 64)
+        k_row_ops<64><<<1, 128>>>(in, softmax_out, row_max, row_sum, centered, col_sum);
+    else if (cols == 128)
+        k_row_ops<128><<<1, 128>>>(in, softmax_out, row_max, row_sum, centered, col_sum);
+    else
+        return -1;
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

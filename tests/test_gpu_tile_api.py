@@ -1,0 +1,106 @@
+"""GPU tests of the C++ tile API (tiledcuda_b200/include): kernels written with GlobalTile / SharedTile /
+TmemTile / RegTile, the tile iterators, the loaders and storers, compute::gemm and the register-tile
+operations, compiled into tests/cpp/libtile_api_tests.so. The cases replay the shapes of the reference's
+single-CTA unit tests (tests/cpp/cell/test_gemm.cu:306-351, test_g2s_load.cu:118-144,
+test_swizzled_copy.cu:399-499, test_softmax.cu:117-163); results are compared on the host with the CPU oracle."""
+import ctypes
+from pathlib import Path
+
+import pytest
+import torch
+
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+LIB = Path(__file__).resolve().parent / "cpp" / "libtile_api_tests.so"
+
+
+@pytest.fixture(scope="module")
+def lib():
+    assert torch.cuda.is_available()
+    assert LIB.exists(), f"{LIB} is missing: build it with `python -m tiledcuda_b200.build --tests`"
+    torch.cuda.set_device(0)
+    return ctypes.CDLL(str(LIB))
+
+
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def test_case_counts(lib):
+    assert lib.tcx_gemm_case_count() == 22 and lib.tcx_roundtrip_case_count() == 12
+
+
+@pytest.mark.parametrize("case", range(12))
+def test_global_shared_round_trip_is_exact(lib, case):
+    """global -> shared (swizzled / interleaved operand layout, or plain fp32) -> global reproduces the data."""
+    src = torch.empty(128 * 256, dtype=torch.float32, device=DEV)
+    dst = torch.full((128 * 256,), -1.0, dtype=torch.float32, device=DEV)
+    rows, cols, elem, cm = (ctypes.c_int() for _ in range(4))
+    # first call only to learn the shape (output is discarded), then the real call on a ramp
+    assert lib.tcx_roundtrip(case, _p(src), _p(dst), ctypes.byref(rows), ctypes.byref(cols), ctypes.byref(elem), ctypes.byref(cm)) == 0
+    torch.cuda.synchronize()
+    n = rows.value * cols.value
+    dtype = torch.float16 if elem.value == 2 else torch.float32
+    ramp = (torch.arange(n, device=DEV) % 2048).to(dtype)   # the `i % 2048` ramp of test_g2s_load.cu:39-40
+    out = torch.full((n,), -1, dtype=dtype, device=DEV)
+    assert lib.tcx_roundtrip(case, _p(ramp), _p(out), ctypes.byref(rows), ctypes.byref(cols), ctypes.byref(elem), ctypes.byref(cm)) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out, ramp)
+
+
+@pytest.mark.parametrize("case", range(22))
+def test_tile_gemm_matches_oracle(lib, case):
+    a_buf = torch.zeros(128 * 512, dtype=torch.float16, device=DEV)
+    b_buf = torch.zeros(256 * 512, dtype=torch.float16, device=DEV)
+    c_buf = torch.full((128 * 256,), float("nan"), device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    m, n, k = (ctypes.c_int() for _ in range(3))
+    # learn the shape from a dry call on zeros
+    assert lib.tcx_tile_gemm(case, _p(a_buf), _p(b_buf), _p(c_buf), _p(status), ctypes.byref(m), ctypes.byref(n), ctypes.byref(k)) == 0
+    torch.cuda.synchronize()
+    M, N, K = m.value, n.value, k.value
+    a, b = oracle.gemm_inputs(M, N, K, seed=100 + case)
+    c = torch.full((M, N), float("nan"), device=DEV)
+    a_dev, b_dev = a.to(DEV), b.to(DEV)   # named, so that they outlive the launch
+    assert lib.tcx_tile_gemm(case, _p(a_dev), _p(b_dev), _p(c), _p(status), ctypes.byref(m), ctypes.byref(n), ctypes.byref(k)) == 0
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    ref = oracle.gemm(a, b)
+    assert oracle.max_abs_err(c, ref) <= 1e-3 and oracle.rel_fro_err(c, ref) <= 1e-5, (M, N, K)
+
+
+@pytest.mark.parametrize("case", range(3))
+def test_tile_b2b_matches_oracle(lib, case):
+    dims = [(64, 64, 64, 64), (128, 128, 128, 128), (32, 128, 64, 48)][case]
+    M, N, K, P = dims
+    a, b, d = oracle.b2b_inputs(M, N, K, P, 1, seed=200 + case)
+    e = torch.full((M, P), float("nan"), device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    m, n, k, p = (ctypes.c_int() for _ in range(4))
+    a_dev, b_dev, d_dev = a[0].to(DEV), b[0].to(DEV), d[0].to(DEV)   # named, so that they outlive the launch
+    rc = lib.tcx_tile_b2b(case, _p(a_dev), _p(b_dev), _p(d_dev), _p(e), _p(status), ctypes.byref(m),
+                          ctypes.byref(n), ctypes.byref(k), ctypes.byref(p))
+    torch.cuda.synchronize()
+    assert rc == 0 and status.item() == 0 and (m.value, n.value, k.value, p.value) == dims
+    assert oracle.within_tolerance(e, oracle.back2back_gemm(a[0], b[0], d[0]))
+
+
+@pytest.mark.parametrize("cols", [16, 64, 128])
+def test_row_operations(lib, cols):
+    g = torch.Generator().manual_seed(42)                       # test_softmax.cu:86-91: uniform[-5, 5), seed 42
+    x = (torch.rand(128, cols, generator=g) * 10 - 5)
+    xd = x.to(DEV)
+    soft = torch.empty(128, cols, device=DEV)
+    centered = torch.empty(128, cols, device=DEV)
+    rmax = torch.empty(128, device=DEV)
+    rsum = torch.empty(128, device=DEV)
+    csum = torch.empty(4, cols, device=DEV)
+    assert lib.tcx_row_ops(cols, _p(xd), _p(soft), _p(rmax), _p(rsum), _p(centered), _p(csum)) == 0
+    torch.cuda.synchronize()
+    assert torch.allclose(soft.cpu(), torch.softmax(x, dim=1), atol=1e-3)   # the reference's bound (test_softmax.cu:113)
+    assert torch.equal(rmax.cpu(), x.max(dim=1).values)
+    assert torch.allclose(rsum.cpu(), x.sum(dim=1), atol=1e-4)
+    assert torch.allclose(centered.cpu(), x - x.max(dim=1, keepdim=True).values, atol=1e-6)
+    assert torch.allclose(csum.cpu(), x.view(4, 32, cols).sum(dim=1), atol=1e-4)

@@ -101,14 +101,47 @@ def build_torch(force: bool = False) -> Path:
     return TORCH_LIB
 
 
+TILE_INCLUDE = PKG / "include"
+TESTS_CPP = PKG.parent / "tests" / "cpp"
+
+
+def build_tile_api_tests(force: bool = False) -> list[Path]:
+    """The libraries the tile-API tests call: device kernels written against tiledcuda_b200/include
+    (nvcc, sm_100a) and the host-side layout checks (g++). Test infrastructure, built in tests/cpp/."""
+    outs = []
+    newest_hdr = _headers_mtime()
+    dev_src, dev_lib = TESTS_CPP / "tile_api_kernels.cu", TESTS_CPP / "libtile_api_tests.so"
+    if dev_src.exists() and (force or not dev_lib.exists() or dev_lib.stat().st_mtime < max(dev_src.stat().st_mtime, newest_hdr)):
+        cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O2", "-std=c++17",
+               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-shared", f"-I{TILE_INCLUDE}", str(dev_src), "-o", str(dev_lib)]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"tile API test kernels failed to build:\n{res.stderr[-6000:]}")
+    if dev_lib.exists():
+        outs.append(dev_lib)
+    host_src, host_lib = TESTS_CPP / "host_layout_checks.cc", TESTS_CPP / "libhost_layout_checks.so"
+    if host_src.exists() and (force or not host_lib.exists() or host_lib.stat().st_mtime < max(host_src.stat().st_mtime, newest_hdr)):
+        cmd = ["g++", "-O1", "-std=c++17", "-fPIC", "-shared", f"-I{TILE_INCLUDE}", str(host_src), "-o", str(host_lib)]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"host layout checks failed to build:\n{res.stderr[-6000:]}")
+    if host_lib.exists():
+        outs.append(host_lib)
+    return outs
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--torch", action="store_true", help="also build the torch op registrations")
     ap.add_argument("--force", action="store_true")
+    ap.add_argument("--tests", action="store_true", help="also build the tile-API test libraries under tests/cpp")
     args = ap.parse_args()
     print(build_core(args.force))
     if args.torch:
         print(build_torch(args.force))
+    if args.tests:
+        for lib in build_tile_api_tests(args.force):
+            print(lib)
     return 0
 
 
