@@ -491,6 +491,7 @@ def run_reference_arm(args, w: Workload, rank: int) -> int:
     dt = (time.perf_counter() - t0) / args.steps
     scale = 1e12 if w.unit == "TFLOP/s" else 1e9
     value = round(units / dt / scale, 4)
+    ref_cuda = reference_cuda_gemm()
     line = {
         "impl": "reference", "metric": w.metric, "value": value, "unit": w.unit, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak",
@@ -500,8 +501,32 @@ def run_reference_arm(args, w: Workload, rank: int) -> int:
         "e2e": {"value": value, "unit": w.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    if ref_cuda is not None:
+        line["reference_cuda_kernel"] = ref_cuda
     print(json.dumps(line), flush=True)
     return 0
+
+
+def reference_cuda_gemm() -> dict | None:
+    """The reference's own CUDA GEMM example (4096^3, its native size; sm_80-style mma.sync kernel compiled
+    unmodified for sm_100a into oracle/_ref/ by oracle/ref_build/Makefile), run once if it was built and a
+    GPU is present. It prints `cuBLAS  TiledCUDA  Ratio` in milliseconds after checking itself against cuBLAS."""
+    exe = ROOT / "oracle" / "_ref" / "ref_gemm_4096"
+    if not exe.exists() or not torch.cuda.is_available():
+        return None
+    try:
+        res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120, cwd=str(exe.parent))
+    except (OSError, subprocess.TimeoutExpired) as e:
+        return {"unavailable": f"{type(e).__name__}"}
+    lines = [l for l in res.stdout.strip().splitlines() if l.strip()]
+    try:
+        cublas_ms, ref_ms, _ = (float(x) for x in lines[-1].split())
+    except (ValueError, IndexError):
+        return {"unavailable": f"exit {res.returncode}: {(res.stdout + res.stderr)[-200:]}"}
+    flops = 2.0 * 4096 ** 3
+    return {"workload": "fp16 GEMM 4096^3 (reference example 02_gemm_all_mem, CTA tile 64x256x32)", "self_check": "Test passed." in res.stdout,
+            "ms": ref_ms, "tflops": round(flops / ref_ms / 1e9, 1), "cublas_hgemm_ms": cublas_ms,
+            "cublas_hgemm_tflops": round(flops / cublas_ms / 1e9, 1)}
 
 
 def _cpu_only_sample(w: Workload):
