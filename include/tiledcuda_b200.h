@@ -47,6 +47,17 @@ int tc_device_status(int* code);
 int tc_gemm_f16_f32(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
                     int64_t ldb, int64_t ldc, tc_stream_t stream);
 
+/* The same GEMM with HOST operands and result (contiguous: lda = ldb = K, ldc = N), for callers whose data
+ * lives in host memory, as the reference's Python examples' does before `.cuda()`
+ * (examples/python/gemm/main.py:47-52). Uploads, products and downloads are pipelined block by block over
+ * both directions of the host link on internal streams; on return everything is queued and `stream` is
+ * ordered after the last download (synchronise it before reading hC). d_workspace is caller-owned device
+ * memory of tc_gemm_host_workspace_bytes(M, N, K) bytes, 256-byte aligned; host buffers should be pinned.
+ * Calls on one device must not overlap (they share the internal streams' events). */
+int64_t tc_gemm_host_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int tc_gemm_f16_f32_host(const void* hA, const void* hB, void* hC, int64_t M, int64_t N, int64_t K, void* d_workspace,
+                         int64_t workspace_bytes, tc_stream_t stream);
+
 /* E[b] (fp32 [M,P]) = fp16(A[b] * B[b]) * D[b] for b in [0,batch): A fp16 [M,K] row-major; B
  * column-major [K,N] stored as [N,K]; D column-major [N,P] stored as [P,N]. The intermediate A*B is
  * accumulated in fp32, rounded to fp16 and never leaves the chip.

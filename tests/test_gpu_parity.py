@@ -329,3 +329,20 @@ def test_unsupported_shapes_raise(cuda_ops):
         cuda_ops.flash_attn(q, q, q, torch.zeros_like(q))
     with pytest.raises(TypeError):
         cuda_ops.gemm(a.float(), a, torch.zeros(128, 128, device=DEV))
+
+
+# ------------------------------------------------------------------------------- host-buffer GEMM
+@pytest.mark.parametrize("m,n,k", [(512, 384, 256), (2304, 2048, 512), (8192, 2560, 264), (1000, 4104, 72)])
+def test_gemm_host_pipelined_matches_oracle(cuda_ops, clean_status, m, n, k):
+    """The host-operand entry point (uploads, block products and downloads overlapped) against the oracle,
+    with guard values around the host result."""
+    a, b = oracle.gemm_inputs(m, n, k)
+    ha, hb = a.pin_memory(), b.pin_memory()
+    hc = torch.full((m, n), float("nan"), dtype=torch.float32).pin_memory()
+    ws = torch.empty(cuda_ops.gemm_host_workspace_bytes(m, n, k), dtype=torch.uint8, device=DEV)
+    cuda_ops.gemm_host(ha, hb, hc, ws)
+    torch.cuda.synchronize()
+    assert_close(hc, oracle.gemm(a, b), max_abs=2e-3, rel_fro=1e-5)
+    cuda_ops.gemm_host(ha, hb, hc, ws)   # a second call reuses the internal streams and events
+    torch.cuda.synchronize()
+    assert_close(hc, oracle.gemm(a, b), max_abs=2e-3, rel_fro=1e-5)

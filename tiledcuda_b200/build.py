@@ -22,7 +22,7 @@ OBJ = PKG / "build"
 LIB = PKG / "libtiledcuda_b200.so"
 TORCH_LIB = PKG / "libtiledcuda.so"
 
-KERNEL_SOURCES = ["host.cu", "scatter_nd.cu", "gemm.cu", "gemm_pair.cu", "chain.cu", "attn.cu", "lstm.cu"]
+KERNEL_SOURCES = ["host.cu", "scatter_nd.cu", "gemm.cu", "gemm_pair.cu", "gemm_host.cu", "chain.cu", "attn.cu", "lstm.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -57,6 +57,35 @@ def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> None:
         )
 
 
+def gemm_host(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, workspace: torch.Tensor) -> None:
+    """c (host, fp32 [M,N]) = a (host, fp16 [M,K]) @ b (host, fp16 [N,K]).T, copies pipelined against the kernel.
+
+    a, b, c are contiguous CPU tensors (pinned for the copies to overlap); workspace is a CUDA uint8 tensor of
+    at least gemm_host_workspace_bytes(M, N, K) bytes on the device that does the work. Everything is queued
+    on return; synchronise the current stream of that device before reading c.
+    """
+    for t, name, dt in ((a, "a", torch.float16), (b, "b", torch.float16), (c, "c", torch.float32)):
+        if t.is_cuda or t.dtype != dt or t.dim() != 2 or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous 2-D CPU tensor of {dt}")
+    if not workspace.is_cuda or not workspace.is_contiguous():
+        raise ValueError("workspace must be a contiguous CUDA tensor")
+    m, k = a.shape
+    n, kb = b.shape
+    if kb != k or tuple(c.shape) != (m, n):
+        raise ValueError(f"shape mismatch: a {tuple(a.shape)}, b {tuple(b.shape)}, c {tuple(c.shape)}")
+    lib = _lib.load()
+    with torch.cuda.device(workspace.device):
+        _lib.check(
+            "tc_gemm_f16_f32_host",
+            lib.tc_gemm_f16_f32_host(_ptr(a), _ptr(b), _ptr(c), m, n, k, _ptr(workspace),
+                                     workspace.numel() * workspace.element_size(), _stream()),
+        )
+
+
+def gemm_host_workspace_bytes(m: int, n: int, k: int) -> int:
+    return int(_lib.load().tc_gemm_host_workspace_bytes(m, n, k))
+
+
 def back2back_gemm(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, e: torch.Tensor) -> None:
     """e (fp32 [.., M, P]) = fp16(a @ b.T) @ d.T, the intermediate kept on chip.
 
