@@ -21,8 +21,8 @@ namespace tcb {
 
 constexpr int kPairBM = 128;      // rows per CTA (256 per pair)
 constexpr int kPairBN = 256;      // columns per pair tile (128 B rows loaded per CTA)
-constexpr int kPairBK = 64;
-constexpr int kPairStages = 6;
+constexpr int kPairBK = 128;     // two 64-element swizzle chunks per operand and stage
+constexpr int kPairStages = 3;
 constexpr int kPairThreads = 192;
 constexpr int kPairABytes = kPairBM * kPairBK * 2;
 constexpr int kPairBBytes = (kPairBN / 2) * kPairBK * 2;
@@ -105,8 +105,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     // the leader's full barrier counts the bytes of both CTAs
                     const uint32_t full_addr = map_to_cta(smem_u32(&bar_full[stage]), 0);
                     if (rank == 0) mbar_arrive_expect_tx(&bar_full[stage], 2 * kPairStageBytes);
-                    tma_load_2d_pair(smem_a + stage * kPairABytes, &tmap_a, full_addr, kb * kPairBK, row_a);
-                    tma_load_2d_pair(smem_b + stage * kPairBBytes, &tmap_b, full_addr, kb * kPairBK, row_b);
+#pragma unroll
+                    for (int c = 0; c < kPairBK / 64; ++c) {
+                        tma_load_2d_pair(smem_a + stage * kPairABytes + c * (kPairBM * 128), &tmap_a, full_addr, kb * kPairBK + c * 64, row_a);
+                        tma_load_2d_pair(smem_b + stage * kPairBBytes + c * ((kPairBN / 2) * 128), &tmap_b, full_addr, kb * kPairBK + c * 64, row_b);
+                    }
                     if (++stage == kPairStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -140,9 +143,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (kPairABytes >> 4);
                     const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (kPairBBytes >> 4);
 #pragma unroll
-                    for (int k = 0; k < kPairBK / 16; ++k)
-                        umma_f16_ss_pair(d_tmem, smem_desc_join(a_lo + static_cast<uint32_t>(k * 2), desc_hi),
-                                         smem_desc_join(b_lo + static_cast<uint32_t>(k * 2), desc_hi), idesc, (kb | k) != 0);
+                    for (int k = 0; k < kPairBK / 16; ++k) {
+                        const uint32_t off_a = static_cast<uint32_t>(((k >> 2) * (kPairBM * 128) + (k & 3) * 32) >> 4);
+                        const uint32_t off_b = static_cast<uint32_t>(((k >> 2) * ((kPairBN / 2) * 128) + (k & 3) * 32) >> 4);
+                        umma_f16_ss_pair(d_tmem, smem_desc_join(a_lo + off_a, desc_hi), smem_desc_join(b_lo + off_b, desc_hi), idesc,
+                                         (kb | k) != 0);
+                    }
                     // the stage is free in both CTAs once these MMAs have read it
                     umma_commit_pair(smem_u32(&bar_empty[stage]));
                     umma_commit_pair(map_to_cta(smem_u32(&bar_empty[stage]), 1));
