@@ -34,6 +34,12 @@ constexpr int kFaTile = 128 * 128 * 2;
 constexpr int kFaChunk = 128 * 64 * 2;
 constexpr int kFaSmem = kFaTile * (2 + kFaStages) + 256 + 1024;
 constexpr float kFaRescaleThreshold = 8.0f;
+#ifndef TCB_FA_POLY_EVERY
+#define TCB_FA_POLY_EVERY 0
+#endif
+constexpr int kFaPolyEvery = TCB_FA_POLY_EVERY;   // 4: one exponential in four on the FMA pipe; 2: every other; 0: none.
+// Measured at s4096 d128: 0 -> 1068, 4 -> 1002, 2 -> 886 TFLOP/s, so the default keeps every exponential on the
+// special-function unit: the softmax warps are short of issue slots, not of ex2 throughput.
 
 struct AttnParams {
     int seq_q;
@@ -266,37 +272,41 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 for (int i = 0; i < 64; ++i)
                     if (i >= n_valid) s[i] = __float_as_uint(masked);
             }
-            // row maximum of scale * s: the extreme of the raw scores times the scale
+            // row maximum of scale * s: the extreme of the raw scores times the scale (three-input max / min)
             float e0 = __uint_as_float(s[0]), e1 = __uint_as_float(s[1]), e2 = __uint_as_float(s[2]), e3 = __uint_as_float(s[3]);
             if (sc >= 0.f) {
 #pragma unroll
-                for (int i = 4; i < 64; i += 4) {
-                    e0 = fmaxf(e0, __uint_as_float(s[i]));
-                    e1 = fmaxf(e1, __uint_as_float(s[i + 1]));
-                    e2 = fmaxf(e2, __uint_as_float(s[i + 2]));
-                    e3 = fmaxf(e3, __uint_as_float(s[i + 3]));
+                for (int i = 4; i < 60; i += 8) {
+                    e0 = fmax3(e0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+                    e1 = fmax3(e1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+                    e2 = fmax3(e2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+                    e3 = fmax3(e3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
                 }
+                e0 = fmax3(e0, __uint_as_float(s[60]), __uint_as_float(s[61]));
+                e1 = fmax3(e1, __uint_as_float(s[62]), __uint_as_float(s[63]));
                 e0 = fmaxf(fmaxf(e0, e1), fmaxf(e2, e3));
             } else {
 #pragma unroll
-                for (int i = 4; i < 64; i += 4) {
-                    e0 = fminf(e0, __uint_as_float(s[i]));
-                    e1 = fminf(e1, __uint_as_float(s[i + 1]));
-                    e2 = fminf(e2, __uint_as_float(s[i + 2]));
-                    e3 = fminf(e3, __uint_as_float(s[i + 3]));
+                for (int i = 4; i < 60; i += 8) {
+                    e0 = fmin3(e0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+                    e1 = fmin3(e1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+                    e2 = fmin3(e2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+                    e3 = fmin3(e3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
                 }
+                e0 = fmin3(e0, __uint_as_float(s[60]), __uint_as_float(s[61]));
+                e1 = fmin3(e1, __uint_as_float(s[62]), __uint_as_float(s[63]));
                 e0 = fminf(fminf(e0, e1), fminf(e2, e3));
             }
             const float mx = e0 * sc;
-            float factor = 1.f;
-            if (g == 0) {
-                m_used = mx;
-            } else if (mx > m_used + kFaRescaleThreshold) {
-                factor = fast_exp2(m_used - mx);
-                m_used = mx;
-            }
-            l_sum *= factor;
-            if (__any_sync(0xffffffffu, factor != 1.f)) {
+            if (g == 0) m_used = mx;
+            // the accumulator is rescaled only when some row of the warp outgrew its reference maximum by 2^8
+            if (__any_sync(0xffffffffu, mx > m_used + kFaRescaleThreshold)) {
+                float factor = 1.f;
+                if (mx > m_used + kFaRescaleThreshold) {
+                    factor = fast_exp2(m_used - mx);
+                    m_used = mx;
+                }
+                l_sum *= factor;
                 // O_t may still be the target of P_t(g-1) V(g-1): wait for it. Seeing s_full of half block g
                 // means the product of half block g-2 is complete, so the parity is unambiguous.
                 if (!mbar_wait_warp(&bar_pv_done[t], static_cast<uint32_t>((g - 1) & 1), abort_word, kDevTimeoutSoftmax)) {
@@ -314,15 +324,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     tmem_st_x16(o_addr + static_cast<uint32_t>(c * 16), r);
                 }
             }
-            // exponentials, row sum, fp16 P written over the first 32 score columns
+            // exponentials, row sum, fp16 P written over the first 32 score columns. One exponential in
+            // kFaPolyEvery may be evaluated on the FMA pipe (poly_exp2) instead of the special-function unit.
             const float neg_m = -m_used;
             float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-                const float a = fast_exp2(fmaf(__uint_as_float(s[2 * i]), sc, neg_m));
-                const float b = fast_exp2(fmaf(__uint_as_float(s[2 * i + 1]), sc, neg_m));
-                const float c2 = fast_exp2(fmaf(__uint_as_float(s[2 * i + 2]), sc, neg_m));
-                const float d2 = fast_exp2(fmaf(__uint_as_float(s[2 * i + 3]), sc, neg_m));
+                const float xa = fmaf(__uint_as_float(s[2 * i]), sc, neg_m);
+                const float xb = fmaf(__uint_as_float(s[2 * i + 1]), sc, neg_m);
+                const float xc = fmaf(__uint_as_float(s[2 * i + 2]), sc, neg_m);
+                const float xd = fmaf(__uint_as_float(s[2 * i + 3]), sc, neg_m);
+                const float a = fast_exp2(xa);
+                const float b = (kFaPolyEvery == 2) ? poly_exp2(xb) : fast_exp2(xb);
+                const float c2 = fast_exp2(xc);
+                const float d2 = (kFaPolyEvery == 2 || kFaPolyEvery == 4) ? poly_exp2(xd) : fast_exp2(xd);
                 sum0 += a;
                 sum1 += b;
                 sum2 += c2;

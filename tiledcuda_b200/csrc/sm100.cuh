@@ -404,6 +404,32 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// 2^x on the FMA pipe, for x <= ~100: floor(x) by the round-down magic-number add, a degree-3 minimax
+// polynomial for 2^frac on [0, 1) (max relative error 7.5e-5, below fp16 resolution), and the integer part
+// added into the exponent field. Takes load off the 16-lane special-function unit, which exponentials of an
+// attention tile otherwise saturate.
+__device__ __forceinline__ float poly_exp2(float x) {
+    x = fmaxf(x, -126.f);
+    float y;
+    asm("add.rm.f32 %0, %1, %2;" : "=f"(y) : "f"(x), "f"(12582912.f));   // 1.5 * 2^23: the low mantissa bits now hold floor(x)
+    const float fl = y - 12582912.f;
+    const float f = x - fl;
+    const float p = fmaf(fmaf(fmaf(0.07802422344684601f, f, 0.22606723010540009f), f, 0.695833683013916f), f, 0.9999251961708069f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(y) << 23));
+}
+
+// max of three (one instruction on sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float fmin3(float a, float b, float c) {
+    float d;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
