@@ -47,6 +47,11 @@ int tc_device_status(int* code);
 int tc_gemm_f16_f32(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
                     int64_t ldb, int64_t ldc, tc_stream_t stream);
 
+/* The same GEMM with bf16 A and B (fp32 accumulate and output). The reference is fp16-only
+ * (include/cell/compute/gemm.hpp:26-29 static_asserts); it has no counterpart there. */
+int tc_gemm_bf16_f32(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                     int64_t ldb, int64_t ldc, tc_stream_t stream);
+
 /* The same GEMM with HOST operands and result (contiguous: lda = ldb = K, ldc = N), for callers whose data
  * lives in host memory, as the reference's Python examples' does before `.cuda()`
  * (examples/python/gemm/main.py:47-52). Uploads, products and downloads are pipelined block by block over

@@ -79,6 +79,17 @@ def test_gemm_linearity_at_sweep_size(cuda_ops, clean_status):
     assert torch.equal(c1[rows].cpu(), oracle.gemm(a1[rows].cpu(), b.cpu()))
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 300, 136), (1024, 1024, 1024), (2250, 2300, 136)])
+def test_gemm_bf16_inputs(cuda_ops, clean_status, m, n, k):
+    """bf16 operands through the same kernels (all three tile variants): exact products, fp32 accumulation."""
+    g = torch.Generator().manual_seed(oracle.SEED)
+    a = (torch.rand(m, k, generator=g) * 2 - 1).bfloat16()
+    b = (torch.rand(n, k, generator=g) * 2 - 1).bfloat16()
+    c = torch.full((m, n), float("nan"), device=DEV)
+    cuda_ops.gemm(a.to(DEV), b.to(DEV), c)
+    assert_close(c, a.float() @ b.float().t(), max_abs=2e-3, rel_fro=1e-5)
+
+
 # --------------------------------------------------------------------------------------- B2B GEMM
 @pytest.mark.parametrize(
     "m,n,k,p,batch",

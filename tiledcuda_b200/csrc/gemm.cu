@@ -46,7 +46,7 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     float* __restrict__ C, int M, int N, int K, int64_t ldc, int tiles_m, int tiles_n,
-                    uint32_t* status) {
+                    uint32_t* status, uint32_t idesc_extra) {
     using S = GemmSmem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align_smem_1024(smem_raw);
@@ -115,7 +115,7 @@ gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_f16_f32(kGemmBM, BN, false, false);
+            const uint32_t idesc = make_idesc_f16_f32(kGemmBM, BN, false, false) | idesc_extra;
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -212,7 +212,7 @@ gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int M, int N, int K, int64_t ldc,
-                       const DeviceInfo* dev, cudaStream_t stream) {
+                       const DeviceInfo* dev, cudaStream_t stream, uint32_t idesc_extra) {
     using S = GemmSmem<BN, STAGES>;
     auto kernel = gemm_f16_f32_kernel<BN, STAGES>;
     static bool configured[64] = {};
@@ -224,20 +224,21 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, float* C, i
     const int tiles_n = (N + BN - 1) / BN;
     const int tiles = tiles_m * tiles_n;
     const int grid = tiles < dev->sm_count ? tiles : dev->sm_count;
-    kernel<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, C, M, N, K, ldc, tiles_m, tiles_n, dev->status_word);
+    kernel<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, C, M, N, K, ldc, tiles_m, tiles_n, dev->status_word, idesc_extra);
     TCB_CUDA(cudaGetLastError());
     return TC_OK;
 }
 
 // 256x256 tiles on CTA pairs (gemm_pair.cu); tb must have been encoded with a 64 x 128 box.
 int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int M, int N, int K, int64_t ldc,
-                     const DeviceInfo* dev, cudaStream_t stream);
+                     const DeviceInfo* dev, cudaStream_t stream, uint32_t idesc_extra);
 
 // The dispatch of tc_gemm_f16_f32 for a caller that brings its own device record (and therefore its own
 // status word) instead of the lazily allocated per-device one. Arguments are trusted: the caller has
 // validated them. Used by entry points that must not allocate.
 int gemm_f16_f32_on(const DeviceInfo* dev, const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K,
-                    int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t stream) {
+                    int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t stream, bool bf16) {
+    const uint32_t extra = bf16 ? kIdescBf16Inputs : 0u;
     const int64_t tiles_pair = ((M + 255) / 256) * ((N + 255) / 256);
     const bool use_pair = tiles_pair >= dev->sm_count / 2;
     const int64_t tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
@@ -248,61 +249,46 @@ int gemm_f16_f32_on(const DeviceInfo* dev, const void* A, const void* B, float* 
         const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
         const uint64_t strides[1] = {static_cast<uint64_t>(lda) * 2};
         const uint32_t box[2] = {kGemmBK, kGemmBM};
-        if (int rc = encode_tmap_f16_sw128(&ta, A, 2, dims, strides, box)) return rc;
+        if (int rc = encode_tmap_f16_sw128(&ta, A, 2, dims, strides, box, bf16)) return rc;
     }
     {
         const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
         const uint64_t strides[1] = {static_cast<uint64_t>(ldb) * 2};
         const uint32_t box[2] = {kGemmBK, bn};
-        if (int rc = encode_tmap_f16_sw128(&tb, B, 2, dims, strides, box)) return rc;
+        if (int rc = encode_tmap_f16_sw128(&tb, B, 2, dims, strides, box, bf16)) return rc;
     }
-    if (use_pair) return launch_gemm_pair(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream);
-    if (use128) return launch_gemm<128, 6>(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream);
-    return launch_gemm<256, 4>(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream);
+    if (use_pair) return launch_gemm_pair(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
+    if (use128) return launch_gemm<128, 6>(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
+    return launch_gemm<256, 4>(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
 }
 
 }  // namespace tcb
 
-extern "C" int tc_gemm_f16_f32(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
-                               int64_t ldb, int64_t ldc, tc_stream_t stream) {
+static int gemm_entry(const char* op, bool bf16, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                      int64_t lda, int64_t ldb, int64_t ldc, tc_stream_t stream) {
     using namespace tcb;
-    TCB_REQUIRE(A && B && C, "gemm: null pointer argument");
-    TCB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: M, N, K must be positive (got %lld, %lld, %lld)", (long long)M,
+    TCB_REQUIRE(A && B && C, "%s: null pointer argument", op);
+    TCB_REQUIRE(M > 0 && N > 0 && K > 0, "%s: M, N, K must be positive (got %lld, %lld, %lld)", op, (long long)M,
                 (long long)N, (long long)K);
-    TCB_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "gemm: a dimension does not fit in 31 bits");
-    TCB_REQUIRE(K % 8 == 0, "gemm: K = %lld is not a multiple of 8 (TMA rows are 16-byte granular)", (long long)K);
-    TCB_REQUIRE(lda >= K && ldb >= K && ldc >= N, "gemm: leading dimension smaller than the row length");
-    TCB_REQUIRE(lda % 8 == 0 && ldb % 8 == 0, "gemm: lda and ldb must be multiples of 8 elements (16 bytes)");
-    TCB_REQUIRE(aligned16(A) && aligned16(B), "gemm: A and B must be 16-byte aligned");
-    TCB_REQUIRE((reinterpret_cast<uintptr_t>(C) & 3u) == 0, "gemm: C must be 4-byte aligned");
-
+    TCB_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "%s: a dimension does not fit in 31 bits", op);
+    TCB_REQUIRE(K % 8 == 0, "%s: K = %lld is not a multiple of 8 (TMA rows are 16-byte granular)", op, (long long)K);
+    TCB_REQUIRE(lda >= K && ldb >= K && ldc >= N, "%s: leading dimension smaller than the row length", op);
+    TCB_REQUIRE(lda % 8 == 0 && ldb % 8 == 0, "%s: lda and ldb must be multiples of 8 elements (16 bytes)", op);
+    TCB_REQUIRE(aligned16(A) && aligned16(B), "%s: A and B must be 16-byte aligned", op);
+    TCB_REQUIRE((reinterpret_cast<uintptr_t>(C) & 3u) == 0, "%s: C must be 4-byte aligned", op);
     const DeviceInfo* dev = nullptr;
     if (int rc = current_device(&dev)) return rc;
-
     // Large problems run 256x256 tiles on CTA pairs; narrow or small ones take lone CTAs with 128x256 or
-    // 128x128 tiles so that more SMs are busy.
-    const int64_t tiles_pair = ((M + 255) / 256) * ((N + 255) / 256);
-    const bool use_pair = tiles_pair >= dev->sm_count / 2;
-    const int64_t tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
-    const bool use128 = !use_pair && ((N <= 128) || (tiles256 < dev->sm_count));
-    const uint32_t bn = (use128 || use_pair) ? 128u : 256u;
+    // 128x128 tiles so that more SMs are busy (the choice is made in gemm_f16_f32_on).
+    return gemm_f16_f32_on(dev, A, B, static_cast<float*>(C), M, N, K, lda, ldb, ldc, static_cast<cudaStream_t>(stream), bf16);
+}
 
-    CUtensorMap ta, tb;
-    {
-        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
-        const uint64_t strides[1] = {static_cast<uint64_t>(lda) * 2};
-        const uint32_t box[2] = {kGemmBK, kGemmBM};
-        if (int rc = encode_tmap_f16_sw128(&ta, A, 2, dims, strides, box)) return rc;
-    }
-    {
-        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
-        const uint64_t strides[1] = {static_cast<uint64_t>(ldb) * 2};
-        const uint32_t box[2] = {kGemmBK, bn};
-        if (int rc = encode_tmap_f16_sw128(&tb, B, 2, dims, strides, box)) return rc;
-    }
-    auto* st = static_cast<cudaStream_t>(stream);
-    if (use_pair) return launch_gemm_pair(ta, tb, static_cast<float*>(C), (int)M, (int)N, (int)K, ldc, dev, st);
-    if (use128)
-        return launch_gemm<128, 6>(ta, tb, static_cast<float*>(C), (int)M, (int)N, (int)K, ldc, dev, st);
-    return launch_gemm<256, 4>(ta, tb, static_cast<float*>(C), (int)M, (int)N, (int)K, ldc, dev, st);
+extern "C" int tc_gemm_f16_f32(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                               int64_t ldb, int64_t ldc, tc_stream_t stream) {
+    return gemm_entry("gemm", false, A, B, C, M, N, K, lda, ldb, ldc, stream);
+}
+
+extern "C" int tc_gemm_bf16_f32(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                                int64_t ldb, int64_t ldc, tc_stream_t stream) {
+    return gemm_entry("gemm_bf16", true, A, B, C, M, N, K, lda, ldb, ldc, stream);
 }

@@ -42,7 +42,8 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tile
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 float* __restrict__ C, int M, int N, int K, int64_t ldc, int tiles_m, int tiles_n, uint32_t* status) {
+                 float* __restrict__ C, int M, int N, int K, int64_t ldc, int tiles_m, int tiles_n, uint32_t* status,
+                 uint32_t idesc_extra) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align_smem_1024(smem_raw);
     uint8_t* smem_a = smem;
@@ -121,7 +122,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader CTA only) ----------------
         if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = make_idesc_f16_f32(2 * kPairBM, kPairBN, false, false);
+            const uint32_t idesc = make_idesc_f16_f32(2 * kPairBM, kPairBN, false, false) | idesc_extra;
             const uint32_t desc_hi = smem_desc_hi_sw128(1024);
             const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem_a), 16);
             const uint32_t b_lo0 = smem_desc_lo(smem_u32(smem_b), 16);
@@ -224,7 +225,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 }
 
 int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int M, int N, int K, int64_t ldc,
-                     const DeviceInfo* dev, cudaStream_t stream) {
+                     const DeviceInfo* dev, cudaStream_t stream, uint32_t idesc_extra) {
     static bool configured[64] = {};
     if (!configured[dev->device]) {
         TCB_CUDA(cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem));
@@ -236,7 +237,7 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int
     const int max_pairs = dev->sm_count / 2;
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
     gemm_pair_kernel<<<2 * pairs, kPairThreads, kPairSmem, stream>>>(ta, tb, C, M, N, K, ldc, tiles_m, tiles_n,
-                                                                    dev->status_word);
+                                                                    dev->status_word, idesc_extra);
     TCB_CUDA(cudaGetLastError());
     return TC_OK;
 }

@@ -66,7 +66,7 @@ static int load_encode() {
 }
 
 int encode_tmap_f16_sw128(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                          const uint64_t* strides_bytes, const uint32_t* box) {
+                          const uint64_t* strides_bytes, const uint32_t* box, bool bf16) {
     if (int rc = load_encode()) return rc;
     cuuint64_t gdim[5];
     cuuint64_t gstride[5];
@@ -78,7 +78,7 @@ int encode_tmap_f16_sw128(CUtensorMap* out, const void* base, int rank, const ui
         estride[i] = 1;
         if (i + 1 < rank) gstride[i] = strides_bytes[i];
     }
-    CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, static_cast<cuuint32_t>(rank),
+    CUresult r = g_encode(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, static_cast<cuuint32_t>(rank),
                           const_cast<void*>(base), gdim, gstride, bdim, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

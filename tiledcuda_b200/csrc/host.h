@@ -43,7 +43,7 @@ int current_device(const DeviceInfo** out);
 // Encodes a tiled fp16 tensor map with 128-byte swizzle. dims/box are innermost-first; strides_bytes has
 // rank-1 entries (stride of dims 1..rank-1). Zero fill outside the tensor.
 int encode_tmap_f16_sw128(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                          const uint64_t* strides_bytes, const uint32_t* box);
+                          const uint64_t* strides_bytes, const uint32_t* box, bool bf16 = false);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

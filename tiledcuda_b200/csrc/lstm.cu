@@ -20,7 +20,7 @@ namespace tcb {
 
 // GEMM dispatch for a caller-supplied device record (gemm.cu).
 int gemm_f16_f32_on(const DeviceInfo* dev, const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K,
-                    int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t stream);
+                    int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t stream, bool bf16);
 
 constexpr int kLstmBM = 128;
 constexpr int kLstmBK = 64;
@@ -506,7 +506,7 @@ extern "C" int tc_lstm_chain_static_f16(const void* W, const void* U, const floa
     LstmWeights lw;
     if (int rc = encode_weights(&lw, dev, W, U, batch, input, hidden)) return rc;
     // The GEMM overwrites every float of the scratch region the steps read, so nothing has to be cleared.
-    if (int rc = gemm_f16_f32_on(dev, x, W, sd->scratch, steps * batch, 4 * hidden, input, input, input, 4 * hidden, st)) return rc;
+    if (int rc = gemm_f16_f32_on(dev, x, W, sd->scratch, steps * batch, 4 * hidden, input, input, input, 4 * hidden, st, false)) return rc;
     const __half* xs = static_cast<const __half*>(x);
     __half* hs = static_cast<__half*>(h_all);
     for (int64_t t = 0; t < steps; ++t) {

@@ -317,6 +317,9 @@ __host__ __device__ constexpr uint32_t make_idesc_f16_f32(int m, int n, bool a_m
            (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// OR-ed into an instruction descriptor to declare A and B as bf16 instead of fp16 (format field value 1).
+constexpr uint32_t kIdescBf16Inputs = (1u << 7) | (1u << 10);
+
 // D[tmem] (+)= A[smem] * B[smem]; issued by one thread.
 __device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                             bool accumulate) {

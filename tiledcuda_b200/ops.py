@@ -35,13 +35,14 @@ def _need(t: torch.Tensor, name: str, dtype: torch.dtype, contiguous: bool = Tru
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> None:
-    """c[M,N] (fp32) = a[M,K] @ b[N,K].T with fp16 inputs and fp32 accumulation.
+    """c[M,N] (fp32) = a[M,K] @ b[N,K].T with fp16 (or bf16) inputs and fp32 accumulation.
 
     `b` is the column-major [K,N] operand of the reference's GEMM stored as [N,K] rows, so the result
     equals `a @ b.t()` (examples/python/gemm/main.py:21). Row strides of a, b, c may exceed the row
     length (leading dimensions); the innermost stride must be 1.
     """
-    for t, name, dt in ((a, "a", torch.float16), (b, "b", torch.float16), (c, "c", torch.float32)):
+    in_dtype = torch.bfloat16 if isinstance(a, torch.Tensor) and a.dtype == torch.bfloat16 else torch.float16
+    for t, name, dt in ((a, "a", in_dtype), (b, "b", in_dtype), (c, "c", torch.float32)):
         _need(t, name, dt, contiguous=False)
         if t.dim() != 2 or t.stride(1) != 1:
             raise ValueError(f"{name} must be 2-D with unit inner stride")
@@ -50,10 +51,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> None:
     if kb != k or tuple(c.shape) != (m, n):
         raise ValueError(f"shape mismatch: a {tuple(a.shape)}, b {tuple(b.shape)}, c {tuple(c.shape)}")
     lib = _lib.load()
+    fn_name = "tc_gemm_bf16_f32" if in_dtype == torch.bfloat16 else "tc_gemm_f16_f32"
     with torch.cuda.device(a.device):
         _lib.check(
-            "tc_gemm_f16_f32",
-            lib.tc_gemm_f16_f32(_ptr(a), _ptr(b), _ptr(c), m, n, k, a.stride(0), b.stride(0), c.stride(0), _stream()),
+            fn_name,
+            getattr(lib, fn_name)(_ptr(a), _ptr(b), _ptr(c), m, n, k, a.stride(0), b.stride(0), c.stride(0), _stream()),
         )
 
 
