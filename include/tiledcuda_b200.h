@@ -83,6 +83,17 @@ int tc_flash_attn_fwd_f16(const void* Q, const void* K, const void* V, void* O, 
                           int64_t heads, int64_t seq_q, int64_t seq_kv, int64_t head_dim, int64_t head_dim_v,
                           float scale, int v_is_transposed, tc_stream_t stream);
 
+/* The same attention with two options the reference's kernel does not have (no counterpart in the
+ * reference: its flash_attention, src/kernels/flash_attn.cu:134-312, is non-causal over
+ * [batch*heads, seq, dim] operands). causal != 0: query row i sees KV rows j <= i + (seq_kv - seq_q),
+ * i.e. the mask is aligned to the bottom-right corner; KV blocks above the diagonal are skipped, a row
+ * that sees no KV row yields zeros and lse = -inf; scale must be non-zero. seq_major != 0: Q, K, V and O
+ * are [batch, seq, heads, dim] (heads interleaved per token, as a fused QKV projection leaves them)
+ * instead of [batch, heads, seq, dim]; not together with a transposed V. lse stays [batch, heads, seq_q]. */
+int tc_flash_attn_fwd_ex_f16(const void* Q, const void* K, const void* V, void* O, float* lse, int64_t batch,
+                             int64_t heads, int64_t seq_q, int64_t seq_kv, int64_t head_dim, int64_t head_dim_v,
+                             float scale, int v_is_transposed, int causal, int seq_major, tc_stream_t stream);
+
 /* One LSTM cell step, gate order (i, f, g, o) as torch.nn.LSTMCell:
  *   gates = x W^T + h_prev U^T + bias;  c_out = sigmoid(f) c_prev + sigmoid(i) tanh(g);
  *   h_out = sigmoid(o) tanh(c_out).
@@ -140,6 +151,15 @@ int tc_lstm_chain_static_f16(const void* W, const void* U, const float* bias, co
  * own test oracle (tests/python/test_scatter_nd.py:46). */
 int tc_scatter_nd(void* data, const void* updates, const void* indices, int idx_is_int64, const int64_t* dims,
                   int rank, int64_t n, int k, int elem_bytes, tc_stream_t stream);
+
+/* ScatterND accumulation: data[idx[t,0], ..., idx[t,k-1], :] += updates[t, :]; repeated tuples add up (in
+ * an unspecified order, so floating-point sums of repeated tuples may differ in the last bits from run
+ * to run; int32 sums are exact). elem_type: 0 = fp32, 1 = fp16, 2 = int32, 3 = fp64. Other arguments and
+ * the treatment of out-of-range tuples as tc_scatter_nd. This is what the reference's kernel does
+ * element by element with atomicAdd (src/kernels/scatter_nd.cu:25-50, the additions at :44-47), whereas
+ * its test oracle (tests/python/test_scatter_nd.py:46) assigns. */
+int tc_scatter_nd_add(void* data, const void* updates, const void* indices, int idx_is_int64, const int64_t* dims,
+                      int rank, int64_t n, int k, int elem_type, tc_stream_t stream);
 
 #ifdef __cplusplus
 }

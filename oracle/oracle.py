@@ -68,19 +68,28 @@ def back2back_gemm(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor) -> torch.T
     return inter @ d32.transpose(-1, -2)
 
 
-def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float | None = None):
+def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float | None = None,
+                    causal: bool = False):
     """(O, LSE) with O = softmax(scale * Q K^T) V in fp32 from fp16 Q [..,Sq,D], K [..,Skv,D], V [..,Skv,Dv].
 
     Reference: mathematically what the blockwise recurrences compute (tests/python/test_flash_attn.py:27-75;
     examples/cpp/03_flash_attention/flash_attn_cpu.hpp:9-100; src/kernels/flash_attn.cu:237-306). The
-    reference applies no scale (scale = 1); the benchmark configuration uses 1/sqrt(D).
+    reference applies no scale (scale = 1); the benchmark configuration uses 1/sqrt(D). causal (which the
+    reference does not have) hides KV row j from query row i when j > i + (Skv - Sq); a row that sees
+    nothing yields zeros and LSE = -inf.
     """
     q32, k32, v32 = (t.detach().cpu().float() for t in (q, k, v))
     if scale is None:
         scale = 1.0 / math.sqrt(q32.shape[-1])
     s = (q32 @ k32.transpose(-1, -2)) * scale
+    if causal:
+        sq, skv = s.shape[-2], s.shape[-1]
+        i = torch.arange(sq).unsqueeze(1)
+        j = torch.arange(skv).unsqueeze(0)
+        s = s.masked_fill(j > i + (skv - sq), float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
-    return torch.softmax(s, dim=-1) @ v32, lse
+    prob = torch.exp(s - lse.unsqueeze(-1).clamp_min(-3.0e38))
+    return prob @ v32, lse
 
 
 def flash_attention_blockwise(q: torch.Tensor, k_t: torch.Tensor, v: torch.Tensor, block_n: int,
@@ -161,6 +170,21 @@ def scatter_nd(data: np.ndarray, indices: np.ndarray, updates: np.ndarray) -> np
     idx = indices.reshape(-1, k).astype(np.int64)
     upd = updates.reshape((idx.shape[0],) + out.shape[k:])
     out[tuple(idx[:, j] for j in range(k))] = upd
+    return out
+
+
+def scatter_nd_add(data: np.ndarray, indices: np.ndarray, updates: np.ndarray) -> np.ndarray:
+    """ScatterND accumulation on a copy of `data`: out[idx[t,...]] += updates[t], repeated tuples adding up.
+
+    Reference: the kernel's per-element atomicAdd (src/kernels/scatter_nd.cu:25-50, additions at :44-47).
+    Sums run in tuple order (np.add.at); the device order is unspecified, so floating-point results with
+    repeated tuples agree to rounding, integer results exactly.
+    """
+    out = np.array(data, copy=True)
+    k = indices.shape[-1]
+    idx = indices.reshape(-1, k).astype(np.int64)
+    upd = updates.reshape((idx.shape[0],) + out.shape[k:])
+    np.add.at(out, tuple(idx[:, j] for j in range(k)), upd)
     return out
 
 

@@ -20,7 +20,7 @@ def declared_symbols():
 
 def test_header_declares_the_expected_entry_points():
     names = declared_symbols()
-    for want in ("tc_gemm_f16_f32", "tc_gemm_bf16_f32", "tc_gemm_f16_f32_host", "tc_lstm_chain_ws_f16", "tc_lstm_chain_static_f16", "tc_b2b_gemm_f16", "tc_flash_attn_fwd_f16", "tc_lstm_cell_f16",
+    for want in ("tc_gemm_f16_f32", "tc_gemm_bf16_f32", "tc_gemm_f16_f32_host", "tc_lstm_chain_ws_f16", "tc_lstm_chain_static_f16", "tc_b2b_gemm_f16", "tc_flash_attn_fwd_f16", "tc_flash_attn_fwd_ex_f16", "tc_scatter_nd_add", "tc_lstm_cell_f16",
                  "tc_lstm_chain_f16", "tc_scatter_nd", "tc_last_error", "tc_device_status", "tc_version"):
         assert want in names
 

@@ -155,6 +155,54 @@ def test_flash_attn_matches_oracle(cuda_ops, clean_status, b, h, sq, skv, d, dv,
     assert (lse.cpu() - ref_lse).abs().max().item() < 1e-3
 
 
+@pytest.mark.parametrize(
+    "b,h,sq,skv,d,dv",
+    [
+        (1, 1, 128, 128, 128, 128), (2, 3, 256, 256, 64, 64), (1, 2, 200, 328, 128, 128), (1, 2, 77, 1001, 80, 48),
+        (1, 1, 1, 8, 16, 16), (1, 2, 640, 640, 128, 128), (1, 1, 300, 200, 64, 64), (2, 4, 1024, 1024, 128, 128),
+        (1, 1, 2048, 2048, 128, 128),
+    ],
+)
+def test_flash_attn_causal_matches_oracle(cuda_ops, clean_status, b, h, sq, skv, d, dv):
+    """Bottom-right aligned causal mask, ragged sizes included; with seq_q > seq_kv the first rows see nothing
+    and come back as zeros with lse = -inf."""
+    q, k, v = oracle.attention_inputs(b, h, sq, skv, d, dv)
+    o = torch.full((b, h, sq, dv), float("nan"), dtype=torch.float16, device=DEV)
+    lse = torch.empty(b, h, sq, device=DEV)
+    cuda_ops.flash_attn(q.to(DEV), k.to(DEV), v.to(DEV), o, lse=lse, causal=True)
+    ref, ref_lse = oracle.flash_attention(q, k, v, causal=True)
+    assert_close(o, ref)
+    seen = torch.isfinite(ref_lse)
+    assert (lse.cpu()[seen] - ref_lse[seen]).abs().max().item() < 1e-3
+    assert torch.isinf(lse.cpu()[~seen]).all()
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("b,h,sq,skv,d,dv", [(2, 3, 256, 384, 64, 64), (1, 5, 100, 100, 128, 128), (2, 8, 1024, 1024, 128, 128)])
+def test_flash_attn_seq_major_operands(cuda_ops, clean_status, causal, b, h, sq, skv, d, dv):
+    """[batch, seq, heads, dim] operands give the same result as the head-major layout."""
+    q, k, v = oracle.attention_inputs(b, h, sq, skv, d, dv)
+    to_sm = lambda t: t.to(DEV).transpose(1, 2).contiguous()
+    o = torch.full((b, sq, h, dv), float("nan"), dtype=torch.float16, device=DEV)
+    lse = torch.empty(b, h, sq, device=DEV)
+    cuda_ops.flash_attn(to_sm(q), to_sm(k), to_sm(v), o, lse=lse, causal=causal, seq_major=True)
+    ref, ref_lse = oracle.flash_attention(q, k, v, causal=causal)
+    assert_close(o.transpose(1, 2), ref)
+    assert (lse.cpu() - ref_lse).abs().max().item() < 1e-3
+    o2 = torch.empty(b, h, sq, dv, dtype=torch.float16, device=DEV)
+    cuda_ops.flash_attn(q.to(DEV), k.to(DEV), v.to(DEV), o2, causal=causal)
+    if sq > 128 or causal:   # same kernel, same arithmetic: bit-identical
+        assert torch.equal(o.transpose(1, 2), o2)
+
+
+def test_flash_attn_ex_rejects_bad_combinations(cuda_ops, clean_status):
+    q = torch.zeros(1, 64, 2, 64, dtype=torch.float16, device=DEV)
+    with pytest.raises(ValueError):
+        cuda_ops.flash_attn(q, q, q, torch.empty_like(q), seq_major=True, v_is_transposed=True)
+    with pytest.raises(RuntimeError, match="non-zero scale"):
+        cuda_ops.flash_attn(q, q, q, torch.empty_like(q), causal=True, scale=0.0)
+
+
 def test_flash_attn_large_scores_need_rescaling(cuda_ops, clean_status):
     """Rows whose maximum grows block after block: exercises the deferred rescale of the accumulator."""
     b, h, s, d = 1, 2, 1024, 64
@@ -326,6 +374,50 @@ def test_scatter_nd_configuration_c5_checksums(cuda_ops, clean_status):
     again = dev.clone()
     cuda_ops.scatter_nd(again, idx.to(DEV), upd.to(DEV))
     assert torch.equal(again.view(torch.int16), dev.view(torch.int16))
+
+
+@pytest.mark.parametrize("index_dtype", [torch.int32, torch.int64])
+@pytest.mark.parametrize("rows,width,n,dtype", [(1000, 8, 3000, torch.float16), (4096, 3, 4096, torch.float16),
+                                                 (257, 5, 1000, torch.float32), (257, 4, 1000, torch.float32),
+                                                 (64, 1, 640, torch.int32), (500, 4, 2000, torch.int32),
+                                                 (100, 2, 700, torch.float64), (100, 3, 700, torch.float64),
+                                                 (1 << 18, 8, 1 << 20, torch.float32)])
+def test_scatter_nd_add_with_repeated_rows(cuda_ops, clean_status, rows, width, n, dtype, index_dtype):
+    """Accumulation with repeated index tuples. Small integer values keep every partial sum exactly
+    representable in each type, so the unspecified order of the additions cannot show and the comparison is
+    bit-exact."""
+    g = torch.Generator().manual_seed(oracle.SEED)
+    table = torch.randint(-8, 8, (rows, width), generator=g).to(dtype)
+    idx = torch.randint(0, rows, (n, 1), generator=g).to(index_dtype)
+    upd = torch.randint(-4, 4, (n, width), generator=g).to(dtype)
+    dev_table = table.to(DEV)
+    cuda_ops.scatter_nd_add(dev_table, idx.to(DEV), upd.to(DEV))
+    want = oracle.scatter_nd_add(table.numpy(), idx.numpy(), upd.numpy())
+    assert dev_table.cpu().numpy().tobytes() == want.tobytes()
+
+
+def test_scatter_nd_add_reference_shape_and_linearity(cuda_ops, clean_status, golden_dir):
+    """The reference test's inputs (tests/python/test_scatter_nd.py:22-54; one tuple occurs twice) in
+    accumulating mode on a zero table: equal to the accumulating oracle (two addends commute, so bit-exact);
+    applying the updates twice doubles the table up to rounding; out-of-range tuples are skipped and reported."""
+    from tiledcuda_b200 import _lib
+
+    g = np.load(golden_dir / "scatter_nd_ref.npz")
+    idx = torch.from_numpy(g["indices"]).to(DEV)
+    upd = torch.from_numpy(g["updates"]).to(DEV)
+    zero = torch.zeros_like(torch.from_numpy(g["data"])).to(DEV)
+    cuda_ops.scatter_nd_add(zero, idx, upd)
+    want = oracle.scatter_nd_add(np.zeros_like(g["data"]), g["indices"], g["updates"])
+    assert zero.cpu().numpy().tobytes() == want.tobytes()
+    cuda_ops.scatter_nd_add(zero, idx, upd)
+    np.testing.assert_allclose(zero.cpu().numpy(), 2 * want, rtol=1e-6, atol=1e-6)
+    data = torch.zeros(16, 8, dtype=torch.float32, device=DEV)
+    bad = torch.tensor([[3], [16], [-1], [3]], dtype=torch.int32, device=DEV)
+    cuda_ops.scatter_nd_add(data, bad, torch.ones(4, 8, device=DEV))
+    assert _lib.device_status() == 16
+    assert data.sum().item() == 16.0 and data[3].sum().item() == 16.0
+    with pytest.raises(TypeError):
+        cuda_ops.scatter_nd_add(torch.zeros(4, 4, dtype=torch.int8, device=DEV), bad[:1], torch.zeros(1, 4, dtype=torch.int8, device=DEV))
 
 
 # ---------------------------------------------------------------------------------- error behaviour

@@ -117,3 +117,33 @@ def test_input_generators_follow_the_configurations():
     a2, _ = oracle.gemm_inputs(32, 16, 64)
     assert torch.equal(a, a2)
     assert math.isclose(oracle.rel_fro_err(a, a), 0.0)
+
+
+def test_oracle_causal_attention_matches_torch_sdpa():
+    """The causal option of the oracle against torch's scaled_dot_product_attention with an explicit mask."""
+    for sq, skv in ((64, 64), (40, 100), (100, 40)):
+        q, k, v = oracle.attention_inputs(1, 2, sq, skv, 32, 32)
+        o, lse = oracle.flash_attention(q, k, v, causal=True)
+        i = torch.arange(sq).unsqueeze(1)
+        j = torch.arange(skv).unsqueeze(0)
+        mask = j <= i + (skv - sq)
+        want = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float(), attn_mask=mask)
+        seen = mask.any(dim=1)
+        assert torch.allclose(o[:, :, seen], want[:, :, seen], atol=1e-5)
+        assert (o[:, :, ~seen] == 0).all() and torch.isinf(lse[:, :, ~seen]).all()
+
+
+def test_oracle_scatter_nd_add_matches_loop_and_torch():
+    """np.add.at restatement against a plain loop and torch.index_put_(accumulate=True)."""
+    rng = np.random.default_rng(oracle.SEED)
+    data = rng.integers(-5, 5, (6, 7, 3)).astype(np.float32)
+    idx = rng.integers(0, (6, 7), (40, 2)).astype(np.int64)
+    upd = rng.integers(-5, 5, (40, 3)).astype(np.float32)
+    got = oracle.scatter_nd_add(data, idx, upd)
+    want = data.copy()
+    for t in range(40):
+        want[idx[t, 0], idx[t, 1]] += upd[t]
+    assert got.tobytes() == want.tobytes()
+    tt = torch.from_numpy(data.copy())
+    tt.index_put_((torch.from_numpy(idx[:, 0]), torch.from_numpy(idx[:, 1])), torch.from_numpy(upd), accumulate=True)
+    assert tt.numpy().tobytes() == want.tobytes()

@@ -29,6 +29,11 @@ SIGNATURES = {
         ctypes.c_int,
         [c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, ctypes.c_float, ctypes.c_int, c_vp],
     ),
+    "tc_flash_attn_fwd_ex_f16": (
+        ctypes.c_int,
+        [c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, ctypes.c_float, ctypes.c_int,
+         ctypes.c_int, ctypes.c_int, c_vp],
+    ),
     "tc_lstm_cell_f16": (ctypes.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp]),
     "tc_lstm_chain_f16": (
         ctypes.c_int,
@@ -44,6 +49,10 @@ SIGNATURES = {
         [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_vp],
     ),
     "tc_scatter_nd": (
+        ctypes.c_int,
+        [c_vp, c_vp, c_vp, ctypes.c_int, ctypes.POINTER(c_i64), ctypes.c_int, c_i64, ctypes.c_int, ctypes.c_int, c_vp],
+    ),
+    "tc_scatter_nd_add": (
         ctypes.c_int,
         [c_vp, c_vp, c_vp, ctypes.c_int, ctypes.POINTER(c_i64), ctypes.c_int, c_i64, ctypes.c_int, ctypes.c_int, c_vp],
     ),

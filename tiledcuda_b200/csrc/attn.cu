@@ -47,6 +47,12 @@ struct AttnParams {
     int dk;
     int dv;
     float scale_log2;
+    int heads;
+    int causal;          // 1: query row i sees KV rows j <= i + causal_off
+    int causal_off;      // seq_kv - seq_q: the last query row sees every KV row
+    int64_t out_stride_b;  // element strides of O over batch, head and query row
+    int64_t out_stride_h;
+    int64_t out_stride_s;
     __half* out;
     float* lse;
     uint32_t* status;
@@ -73,10 +79,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int q0 = blockIdx.x * (2 * kFaBM);
+    // with a causal mask the CTAs with the most KV blocks are scheduled first
+    const int q_blk = p.causal ? static_cast<int>(gridDim.x - 1 - blockIdx.x) : static_cast<int>(blockIdx.x);
+    const int q0 = q_blk * (2 * kFaBM);
     const int bh = blockIdx.y;
-    const int n_blocks = (p.seq_kv + kFaBN - 1) / kFaBN;   // 128-row K / V blocks (TMA granularity)
-    const int n_halves = (p.seq_kv + 63) / 64;             // 64-row half blocks (score granularity)
+    const int head = bh % p.heads;
+    const int bat = bh / p.heads;
+    // KV rows this CTA needs: all of them, or up to the diagonal of its last query row
+    const int kv_len = p.causal ? max(0, min(p.seq_kv, min(p.seq_q, q0 + 2 * kFaBM) + p.causal_off)) : p.seq_kv;
+    const int n_halves = max(1, (kv_len + 63) / 64);       // 64-row half blocks (score granularity)
+    const int n_blocks = (n_halves + 1) / 2;               // 128-row K / V blocks (TMA granularity)
     const int k_chunks = (p.dk + 63) / 64;
     const int v_chunks = (p.dv + 63) / 64;
     const int k_steps = p.dk / 16;
@@ -119,7 +131,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             const int n_tiles = two_tiles ? 2 : 1;
             // Q tile 0, then K_0 so that the first MMA can start, then Q tile 1
             mbar_arrive_expect_tx(&bar_q_full[0], k_bytes);
-            for (int c = 0; c < k_chunks; ++c) tma_load_3d(s_q + c * kFaChunk, &tmap_q, &bar_q_full[0], c * 64, q0, bh);
+            for (int c = 0; c < k_chunks; ++c) tma_load_4d(s_q + c * kFaChunk, &tmap_q, &bar_q_full[0], c * 64, q0, head, bat);
             bool q1_sent = false;
             for (int e = 0; e < 2 * n_blocks; ++e) {
                 const int stage = e % kFaStages;
@@ -130,21 +142,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 if ((e & 1) == 0) {
                     mbar_arrive_expect_tx(&bar_kv_full[stage], k_bytes);
                     for (int c = 0; c < k_chunks; ++c)
-                        tma_load_3d(dst + c * kFaChunk, &tmap_k, &bar_kv_full[stage], c * 64, j * kFaBN, bh);
+                        tma_load_4d(dst + c * kFaChunk, &tmap_k, &bar_kv_full[stage], c * 64, j * kFaBN, head, bat);
                 } else {
                     mbar_arrive_expect_tx(&bar_kv_full[stage], v_bytes);
                     if (kVTrans) {
                         for (int c = 0; c < 2; ++c)
-                            tma_load_3d(dst + c * (p.dv * 128), &tmap_v, &bar_kv_full[stage], j * kFaBN + c * 64, 0, bh);
+                            tma_load_4d(dst + c * (p.dv * 128), &tmap_v, &bar_kv_full[stage], j * kFaBN + c * 64, 0, head, bat);
                     } else {
                         for (int c = 0; c < v_chunks; ++c)
-                            tma_load_3d(dst + c * kFaChunk, &tmap_v, &bar_kv_full[stage], c * 64, j * kFaBN, bh);
+                            tma_load_4d(dst + c * kFaChunk, &tmap_v, &bar_kv_full[stage], c * 64, j * kFaBN, head, bat);
                     }
                 }
                 if (!q1_sent && n_tiles == 2) {
                     mbar_arrive_expect_tx(&bar_q_full[1], k_bytes);
                     for (int c = 0; c < k_chunks; ++c)
-                        tma_load_3d(s_q + kFaTile + c * kFaChunk, &tmap_q, &bar_q_full[1], c * 64, q0 + kFaBM, bh);
+                        tma_load_4d(s_q + kFaTile + c * kFaChunk, &tmap_q, &bar_q_full[1], c * 64, q0 + kFaBM, head, bat);
                     q1_sent = true;
                 }
             }
@@ -259,7 +271,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
             tc_fence_after_sync();
             const uint32_t s_addr = s_base + static_cast<uint32_t>(h * 64);
-            const int n_valid = min(64, p.seq_kv - g * 64);
+            // columns of this half block the row may see: the end of the sequence and, with a causal mask, the diagonal
+            int n_valid = min(64, p.seq_kv - g * 64);
+            if (p.causal) n_valid = min(n_valid, row + p.causal_off + 1 - g * 64);
 
             // the 64 scores of this row and half block into registers
             uint32_t s[64];
@@ -298,7 +312,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 e0 = fminf(fminf(e0, e1), fminf(e2, e3));
             }
             const float mx = e0 * sc;
-            if (g == 0) m_used = mx;
+            if (g == 0) m_used = fmaxf(mx, -1e30f);   // finite even for a row that sees no KV row at all
             // the accumulator is rescaled only when some row of the warp outgrew its reference maximum by 2^8
             if (__any_sync(0xffffffffu, mx > m_used + kFaRescaleThreshold)) {
                 float factor = 1.f;
@@ -356,8 +370,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         // ---------------- epilogue ----------------
         if (ok && mbar_wait_warp(&bar_o_full[t], 0, abort_word, kDevTimeoutEpilogue)) {
             tc_fence_after_sync();
-            const float inv_l = 1.f / l_sum;
+            const float inv_l = l_sum > 0.f ? 1.f / l_sum : 0.f;   // a fully masked row yields zeros
             const int64_t out_row = static_cast<int64_t>(bh) * p.seq_q + row;
+            __half* out_ptr = p.out + bat * p.out_stride_b + head * p.out_stride_h + row * p.out_stride_s;
 #pragma unroll 1
             for (int c = 0; c < p.dv / 16; ++c) {
                 uint32_t r[16];
@@ -368,7 +383,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
                         h[i] = pack_half2(__uint_as_float(r[2 * i]) * inv_l, __uint_as_float(r[2 * i + 1]) * inv_l);
-                    uint4* dst = reinterpret_cast<uint4*>(p.out + out_row * p.dv + c * 16);
+                    uint4* dst = reinterpret_cast<uint4*>(out_ptr + c * 16);
                     dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
                     dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
                 }
@@ -387,25 +402,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     if (threadIdx.x == 0 && *abort_word != 0) atomicMax(p.status, *abort_word);
 }
 
-static int encode_attn_3d(CUtensorMap* out, const void* base, int64_t batch, int64_t rows, int64_t cols, uint32_t box_rows) {
-    const uint64_t dims[3] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(rows), static_cast<uint64_t>(batch)};
-    const uint64_t strides[2] = {static_cast<uint64_t>(cols) * 2, static_cast<uint64_t>(rows) * static_cast<uint64_t>(cols) * 2};
-    const uint32_t box[3] = {64, box_rows, 1};
-    return encode_tmap_f16_sw128(out, base, 3, dims, strides, box);
+// 4-D map over (column, row, head, batch) with element strides for row, head and batch.
+static int encode_attn_4d(CUtensorMap* out, const void* base, int64_t batch, int64_t heads, int64_t rows, int64_t cols,
+                          int64_t stride_row, int64_t stride_head, int64_t stride_batch, uint32_t box_rows) {
+    const uint64_t dims[4] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(rows), static_cast<uint64_t>(heads),
+                              static_cast<uint64_t>(batch)};
+    const uint64_t strides[3] = {static_cast<uint64_t>(stride_row) * 2, static_cast<uint64_t>(stride_head) * 2,
+                                 static_cast<uint64_t>(stride_batch) * 2};
+    const uint32_t box[4] = {64, box_rows, 1, 1};
+    return encode_tmap_f16_sw128(out, base, 4, dims, strides, box);
 }
 
-// Launcher used by tc_flash_attn_fwd_f16 for seq_q > 128. Arguments are validated by the caller.
-int launch_attn_pingpong(const void* Q, const void* K, const void* V, void* O, float* lse, int64_t bh, int64_t seq_q,
-                         int64_t seq_kv, int64_t dk, int64_t dv, float scale, bool v_trans, cudaStream_t stream) {
+// Launcher behind the attention entry points. Arguments are validated by the caller. seq_major: operands
+// are [batch, seq, heads, dim] instead of [batch, heads, seq, dim] (not with a transposed V).
+int launch_attn_pingpong(const void* Q, const void* K, const void* V, void* O, float* lse, int64_t batch, int64_t heads,
+                         int64_t seq_q, int64_t seq_kv, int64_t dk, int64_t dv, float scale, bool v_trans, bool causal,
+                         bool seq_major, cudaStream_t stream) {
     const DeviceInfo* dev = nullptr;
     if (int rc = current_device(&dev)) return rc;
     CUtensorMap tq, tk, tv;
-    if (int rc = encode_attn_3d(&tq, Q, bh, seq_q, dk, kFaBM)) return rc;
-    if (int rc = encode_attn_3d(&tk, K, bh, seq_kv, dk, kFaBN)) return rc;
+    auto encode = [&](CUtensorMap* m, const void* base, int64_t rows, int64_t cols, uint32_t box_rows) {
+        if (seq_major) return encode_attn_4d(m, base, batch, heads, rows, cols, heads * cols, cols, rows * heads * cols, box_rows);
+        return encode_attn_4d(m, base, batch, heads, rows, cols, cols, rows * cols, heads * rows * cols, box_rows);
+    };
+    if (int rc = encode(&tq, Q, seq_q, dk, kFaBM)) return rc;
+    if (int rc = encode(&tk, K, seq_kv, dk, kFaBN)) return rc;
     if (v_trans) {
-        if (int rc = encode_attn_3d(&tv, V, bh, dv, seq_kv, static_cast<uint32_t>(dv))) return rc;
+        if (int rc = encode(&tv, V, dv, seq_kv, static_cast<uint32_t>(dv))) return rc;
     } else {
-        if (int rc = encode_attn_3d(&tv, V, bh, seq_kv, dv, kFaBN)) return rc;
+        if (int rc = encode(&tv, V, seq_kv, dv, kFaBN)) return rc;
     }
     AttnParams p;
     p.seq_q = static_cast<int>(seq_q);
@@ -413,10 +438,16 @@ int launch_attn_pingpong(const void* Q, const void* K, const void* V, void* O, f
     p.dk = static_cast<int>(dk);
     p.dv = static_cast<int>(dv);
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.heads = static_cast<int>(heads);
+    p.causal = causal ? 1 : 0;
+    p.causal_off = static_cast<int>(seq_kv - seq_q);
+    p.out_stride_s = seq_major ? heads * dv : dv;
+    p.out_stride_h = seq_major ? dv : seq_q * dv;
+    p.out_stride_b = heads * seq_q * dv;
     p.out = static_cast<__half*>(O);
     p.lse = lse;
     p.status = dev->status_word;
-    const dim3 grid(static_cast<unsigned>((seq_q + 2 * kFaBM - 1) / (2 * kFaBM)), static_cast<unsigned>(bh));
+    const dim3 grid(static_cast<unsigned>((seq_q + 2 * kFaBM - 1) / (2 * kFaBM)), static_cast<unsigned>(batch * heads));
     static bool configured[2][64] = {};
     if (v_trans) {
         if (!configured[1][dev->device]) {

@@ -395,9 +395,33 @@ static int check_chain_dims(const char* op, int64_t batch, int64_t rows, int64_t
     return TC_OK;
 }
 
-// Two-tile ping-pong attention kernel (attn.cu), used when there is more than one 128-row tile of queries.
-int launch_attn_pingpong(const void* Q, const void* K, const void* V, void* O, float* lse, int64_t bh, int64_t seq_q,
-                         int64_t seq_kv, int64_t dk, int64_t dv, float scale, bool v_trans, cudaStream_t stream);
+// Two-tile ping-pong attention kernel (attn.cu), used when there is more than one 128-row tile of queries,
+// a causal mask or sequence-major operands.
+int launch_attn_pingpong(const void* Q, const void* K, const void* V, void* O, float* lse, int64_t batch, int64_t heads,
+                         int64_t seq_q, int64_t seq_kv, int64_t dk, int64_t dv, float scale, bool v_trans, bool causal,
+                         bool seq_major, cudaStream_t stream);
+
+static int attn_entry(const char* op, const void* Q, const void* K, const void* V, void* O, float* lse, int64_t batch,
+                      int64_t heads, int64_t seq_q, int64_t seq_kv, int64_t head_dim, int64_t head_dim_v, float scale,
+                      int v_is_transposed, int causal, int seq_major, tc_stream_t stream) {
+    TCB_REQUIRE(Q && K && V && O, "%s: null pointer argument", op);
+    TCB_REQUIRE(batch > 0 && heads > 0, "%s: batch and heads must be positive", op);
+    if (int rc = check_chain_dims(op, batch * heads, seq_q, seq_kv, head_dim, head_dim_v)) return rc;
+    TCB_REQUIRE(!v_is_transposed || seq_kv % 8 == 0, "%s: seq_kv = %lld must be a multiple of 8 for transposed V", op,
+                (long long)seq_kv);
+    TCB_REQUIRE(!(v_is_transposed && seq_major), "%s: a transposed V is not supported with sequence-major operands", op);
+    TCB_REQUIRE(head_dim % 8 == 0 && head_dim_v % 8 == 0, "%s: head dims must be multiples of 8", op);
+    TCB_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(V) && aligned16(O), "%s: pointers must be 16-byte aligned", op);
+    TCB_REQUIRE(isfinite(scale), "%s: scale is not finite", op);
+    TCB_REQUIRE(!causal || scale != 0.f, "%s: a causal mask needs a non-zero scale", op);
+    auto* st = static_cast<cudaStream_t>(stream);
+    if (seq_q > kChBM || causal || seq_major)
+        return launch_attn_pingpong(Q, K, V, O, lse, batch, heads, seq_q, seq_kv, head_dim, head_dim_v, scale,
+                                    v_is_transposed != 0, causal != 0, seq_major != 0, st);
+    if (v_is_transposed)
+        return launch_chain<true, true>(Q, K, V, O, lse, batch * heads, seq_q, seq_kv, head_dim, head_dim_v, scale, st);
+    return launch_chain<true, false>(Q, K, V, O, lse, batch * heads, seq_q, seq_kv, head_dim, head_dim_v, scale, st);
+}
 
 }  // namespace tcb
 
@@ -414,19 +438,14 @@ extern "C" int tc_b2b_gemm_f16(const void* A, const void* B, const void* D, void
 extern "C" int tc_flash_attn_fwd_f16(const void* Q, const void* K, const void* V, void* O, float* lse, int64_t batch,
                                      int64_t heads, int64_t seq_q, int64_t seq_kv, int64_t head_dim,
                                      int64_t head_dim_v, float scale, int v_is_transposed, tc_stream_t stream) {
-    using namespace tcb;
-    TCB_REQUIRE(Q && K && V && O, "flash_attn_fwd: null pointer argument");
-    TCB_REQUIRE(batch > 0 && heads > 0, "flash_attn_fwd: batch and heads must be positive");
-    if (int rc = check_chain_dims("flash_attn_fwd", batch * heads, seq_q, seq_kv, head_dim, head_dim_v)) return rc;
-    TCB_REQUIRE(!v_is_transposed || seq_kv % 8 == 0, "flash_attn_fwd: seq_kv = %lld must be a multiple of 8 for transposed V",
-                (long long)seq_kv);
-    TCB_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(V) && aligned16(O), "flash_attn_fwd: pointers must be 16-byte aligned");
-    TCB_REQUIRE(isfinite(scale), "flash_attn_fwd: scale is not finite");
-    auto* st = static_cast<cudaStream_t>(stream);
-    if (seq_q > kChBM)
-        return launch_attn_pingpong(Q, K, V, O, lse, batch * heads, seq_q, seq_kv, head_dim, head_dim_v, scale,
-                                    v_is_transposed != 0, st);
-    if (v_is_transposed)
-        return launch_chain<true, true>(Q, K, V, O, lse, batch * heads, seq_q, seq_kv, head_dim, head_dim_v, scale, st);
-    return launch_chain<true, false>(Q, K, V, O, lse, batch * heads, seq_q, seq_kv, head_dim, head_dim_v, scale, st);
+    return tcb::attn_entry("flash_attn_fwd", Q, K, V, O, lse, batch, heads, seq_q, seq_kv, head_dim, head_dim_v, scale,
+                           v_is_transposed, 0, 0, stream);
+}
+
+extern "C" int tc_flash_attn_fwd_ex_f16(const void* Q, const void* K, const void* V, void* O, float* lse, int64_t batch,
+                                        int64_t heads, int64_t seq_q, int64_t seq_kv, int64_t head_dim,
+                                        int64_t head_dim_v, float scale, int v_is_transposed, int causal,
+                                        int seq_major, tc_stream_t stream) {
+    return tcb::attn_entry("flash_attn_fwd_ex", Q, K, V, O, lse, batch, heads, seq_q, seq_kv, head_dim, head_dim_v, scale,
+                           v_is_transposed, causal, seq_major, stream);
 }

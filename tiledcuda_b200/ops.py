@@ -119,21 +119,35 @@ def flash_attn(
     scale: float | None = None,
     lse: torch.Tensor | None = None,
     v_is_transposed: bool = False,
+    causal: bool = False,
+    seq_major: bool = False,
 ) -> None:
-    """o = softmax(scale * q k^T) v per (batch, head); non-causal; fp32 statistics.
+    """o = softmax(scale * q k^T) v per (batch, head); fp32 statistics.
 
     q [B,H,Sq,D], k [B,H,Skv,D], o [B,H,Sq,Dv] fp16; v [B,H,Skv,Dv], or [B,H,Dv,Skv] when
-    v_is_transposed. scale defaults to 1/sqrt(D). lse, if given, is fp32 [B,H,Sq].
+    v_is_transposed. With seq_major the four tensors are [B,S,H,D] instead. scale defaults to
+    1/sqrt(D). lse, if given, is fp32 [B,H,Sq]. causal: query row i sees KV rows
+    j <= i + (Skv - Sq); a row that sees none comes back as zeros.
     """
     for t, name in ((q, "q"), (k, "k"), (v, "v"), (o, "o")):
         _need(t, name, torch.float16)
         if t.dim() != 4:
             raise ValueError(f"{name} must be 4-D [batch, heads, seq, dim]")
-    b, h, sq, d = q.shape
-    skv = k.shape[2]
-    dv = v.shape[2] if v_is_transposed else v.shape[3]
-    v_expect = (b, h, dv, skv) if v_is_transposed else (b, h, skv, dv)
-    if tuple(k.shape) != (b, h, skv, d) or tuple(v.shape) != v_expect or tuple(o.shape) != (b, h, sq, dv):
+    if seq_major:
+        if v_is_transposed:
+            raise ValueError("a transposed v is not supported with seq_major operands")
+        b, sq, h, d = q.shape
+        skv = k.shape[1]
+        dv = v.shape[3]
+        k_expect, v_expect, o_expect = (b, skv, h, d), (b, skv, h, dv), (b, sq, h, dv)
+    else:
+        b, h, sq, d = q.shape
+        skv = k.shape[2]
+        dv = v.shape[2] if v_is_transposed else v.shape[3]
+        k_expect = (b, h, skv, d)
+        v_expect = (b, h, dv, skv) if v_is_transposed else (b, h, skv, dv)
+        o_expect = (b, h, sq, dv)
+    if tuple(k.shape) != k_expect or tuple(v.shape) != v_expect or tuple(o.shape) != o_expect:
         raise ValueError(f"shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}, o {tuple(o.shape)}")
     if lse is not None:
         _need(lse, "lse", torch.float32)
@@ -143,13 +157,22 @@ def flash_attn(
         scale = 1.0 / math.sqrt(d)
     lib = _lib.load()
     with torch.cuda.device(q.device):
-        _lib.check(
-            "tc_flash_attn_fwd_f16",
-            lib.tc_flash_attn_fwd_f16(
-                _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), b, h, sq, skv, d, dv, float(scale),
-                int(bool(v_is_transposed)), _stream(),
-            ),
-        )
+        if causal or seq_major:
+            _lib.check(
+                "tc_flash_attn_fwd_ex_f16",
+                lib.tc_flash_attn_fwd_ex_f16(
+                    _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), b, h, sq, skv, d, dv, float(scale),
+                    int(bool(v_is_transposed)), int(bool(causal)), int(bool(seq_major)), _stream(),
+                ),
+            )
+        else:
+            _lib.check(
+                "tc_flash_attn_fwd_f16",
+                lib.tc_flash_attn_fwd_f16(
+                    _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), b, h, sq, skv, d, dv, float(scale),
+                    int(bool(v_is_transposed)), _stream(),
+                ),
+            )
 
 
 def flash_attention_fwd(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, O: torch.Tensor, m: int, n: int, k: int, p: int) -> None:
@@ -273,13 +296,10 @@ def lstm_chain_workspace_bytes(steps: int, batch: int, hidden: int) -> int:
     return int(_lib.load().tc_lstm_chain_workspace_bytes(steps, batch, hidden))
 
 
-def scatter_nd(data: torch.Tensor, indices: torch.Tensor, updates: torch.Tensor) -> None:
-    """data[indices[t, 0], ..., indices[t, k-1]] = updates[t] for every index tuple t (in place).
+_SCATTER_ADD_TYPES = {torch.float32: 0, torch.float16: 1, torch.int32: 2, torch.float64: 3}
 
-    data is N-D and contiguous; indices is int32 or int64 [..., k]; updates holds one slice
-    data.shape[k:] per tuple. Tuples must be unique for a deterministic result. Argument order follows
-    the reference's Python wrapper (pytiledcuda/__init__.py:6-8): data, indices, updates.
-    """
+
+def _scatter_args(data: torch.Tensor, indices: torch.Tensor, updates: torch.Tensor):
     if not data.is_cuda or not indices.is_cuda or not updates.is_cuda:
         raise ValueError("scatter_nd needs CUDA tensors (there is no CPU path)")
     if indices.dtype not in (torch.int32, torch.int64):
@@ -300,10 +320,39 @@ def scatter_nd(data: torch.Tensor, indices: torch.Tensor, updates: torch.Tensor)
     if updates.numel() != n * slice_elems:
         raise ValueError(f"updates has {updates.numel()} elements, expected {n} slices of {slice_elems}")
     dims = (ctypes.c_int64 * data.dim())(*data.shape)
+    return dims, n, k
+
+
+def scatter_nd(data: torch.Tensor, indices: torch.Tensor, updates: torch.Tensor) -> None:
+    """data[indices[t, 0], ..., indices[t, k-1]] = updates[t] for every index tuple t (in place).
+
+    data is N-D and contiguous; indices is int32 or int64 [..., k]; updates holds one slice
+    data.shape[k:] per tuple. Tuples must be unique for a deterministic result. Argument order follows
+    the reference's Python wrapper (pytiledcuda/__init__.py:6-8): data, indices, updates.
+    """
+    dims, n, k = _scatter_args(data, indices, updates)
     lib = _lib.load()
     with torch.cuda.device(data.device):
         _lib.check(
             "tc_scatter_nd",
             lib.tc_scatter_nd(_ptr(data), _ptr(updates), _ptr(indices), int(indices.dtype == torch.int64), dims,
                               data.dim(), n, k, data.element_size(), _stream()),
+        )
+
+
+def scatter_nd_add(data: torch.Tensor, indices: torch.Tensor, updates: torch.Tensor) -> None:
+    """data[indices[t, 0], ..., indices[t, k-1]] += updates[t] (in place); repeated tuples add up.
+
+    What the reference's kernel does with one atomicAdd per element (src/kernels/scatter_nd.cu:44-47).
+    fp32, fp16, int32 and fp64 tables; arguments as scatter_nd.
+    """
+    if data.dtype not in _SCATTER_ADD_TYPES:
+        raise TypeError(f"scatter_nd_add supports {sorted(str(t) for t in _SCATTER_ADD_TYPES)}, got {data.dtype}")
+    dims, n, k = _scatter_args(data, indices, updates)
+    lib = _lib.load()
+    with torch.cuda.device(data.device):
+        _lib.check(
+            "tc_scatter_nd_add",
+            lib.tc_scatter_nd_add(_ptr(data), _ptr(updates), _ptr(indices), int(indices.dtype == torch.int64), dims,
+                                  data.dim(), n, k, _SCATTER_ADD_TYPES[data.dtype], _stream()),
         )
