@@ -79,6 +79,29 @@ def test_gemm_linearity_at_sweep_size(cuda_ops, clean_status):
     assert torch.equal(c1[rows].cpu(), oracle.gemm(a1[rows].cpu(), b.cpu()))
 
 
+def test_gemm_tall_pair_tiles_ragged_and_linear(cuda_ops, clean_status):
+    """Operands far beyond L2 take the 512x256 pair tiles: ragged M and N with guard bands, sampled rows
+    against the oracle (first, middle and last row tiles, both CTAs and both accumulator halves), and
+    exact linearity over the whole result with small dyadic values."""
+    m, n, k = 16384 + 328, 16384 - 56, 8192
+    g = torch.Generator(device=DEV).manual_seed(oracle.SEED)
+    mk = lambda r: (torch.randint(-8, 8, (r, k), generator=g, device=DEV, dtype=torch.int32).float() / 8).half()
+    a1, a2, b = mk(m), mk(m), mk(n)
+    store = torch.full((m + 2, n + 8), -7.0, device=DEV)
+    c1 = store[1:m + 1, 4:n + 4]
+    cuda_ops.gemm(a1, b, c1)
+    rows = torch.cat([torch.arange(0, 512, 37), torch.arange(8192 + 100, 8192 + 612, 41), torch.arange(m - 330, m, 11)]).to(DEV)
+    want = oracle.gemm(a1[rows].cpu(), b.cpu())
+    assert torch.equal(c1[rows].cpu(), want)   # dyadic values: exact in fp32
+    assert (store[0] == -7.0).all() and (store[-1] == -7.0).all()
+    assert (store[:, :4] == -7.0).all() and (store[:, -4:] == -7.0).all()
+    c2 = torch.empty(m, n, device=DEV)
+    cuda_ops.gemm(a2, b, c2)
+    c2 += c1
+    cuda_ops.gemm(a1 + a2, b, c1)
+    assert torch.equal(c1, c2)
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 300, 136), (1024, 1024, 1024), (2250, 2300, 136)])
 def test_gemm_bf16_inputs(cuda_ops, clean_status, m, n, k):
     """bf16 operands through the same kernels (all three tile variants): exact products, fp32 accumulation."""

@@ -13,6 +13,8 @@
 // Stands in for the reference's `gemm` (examples/cpp/01_gemm/02_gemm_all_mem/gemm.hpp:92-155: cp.async
 // -> swizzled smem -> ldmatrix -> mma.sync, single stage) and cell::compute::gemm
 // (include/cell/compute/gemm.hpp:19-88).
+#include <stdlib.h>
+
 #include "host.h"
 #include "sm100.cuh"
 
@@ -233,6 +235,10 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, float* C, i
 int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int M, int N, int K, int64_t ldc,
                      const DeviceInfo* dev, cudaStream_t stream, uint32_t idesc_extra);
 
+// 512x256 tiles on CTA pairs (gemm_pair.cu); same tensor maps as launch_gemm_pair.
+int launch_gemm_pair_tall(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int M, int N, int K, int64_t ldc,
+                          const DeviceInfo* dev, cudaStream_t stream, uint32_t idesc_extra);
+
 // The dispatch of tc_gemm_f16_f32 for a caller that brings its own device record (and therefore its own
 // status word) instead of the lazily allocated per-device one. Arguments are trusted: the caller has
 // validated them. Used by entry points that must not allocate.
@@ -257,7 +263,20 @@ int gemm_f16_f32_on(const DeviceInfo* dev, const void* A, const void* B, float* 
         const uint32_t box[2] = {kGemmBK, bn};
         if (int rc = encode_tmap_f16_sw128(&tb, B, 2, dims, strides, box, bf16)) return rc;
     }
-    if (use_pair) return launch_gemm_pair(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
+    if (use_pair) {
+        // Operands far larger than L2 take 512x256 tiles, which fetch a quarter fewer operand bytes per FLOP
+        // (measured at 16384^3: 1369 against 1262 TFLOP/s; at 8192^3 the two are equal, below that the
+        // coarser tiles lose to wave quantisation).
+        const int64_t operand_bytes = (M + N) * K * 2;
+        const int64_t tiles_tall = ((M + 511) / 512) * ((N + 255) / 256);
+        bool use_tall = operand_bytes >= (512ll << 20) && K >= 2048 && tiles_tall >= 2 * (dev->sm_count / 2);
+        if (const char* force = getenv("TC_GEMM_PAIR_TILE")) {   // "tall" or "square": overrides the choice (tuning aid)
+            if (force[0] == 't') use_tall = true;
+            if (force[0] == 's') use_tall = false;
+        }
+        if (use_tall) return launch_gemm_pair_tall(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
+        return launch_gemm_pair(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
+    }
     if (use128) return launch_gemm<128, 6>(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
     return launch_gemm<256, 4>(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
 }

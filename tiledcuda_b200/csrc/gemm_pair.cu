@@ -224,6 +224,226 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (threadIdx.x == 0 && *abort_word != 0) atomicMax(status, *abort_word);
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Tall variant: 512x256 output tiles per pair. Each CTA owns 256 rows as two 128-row halves with one
+// 256-column accumulator each (all 512 TMEM columns), so a 64-wide K block brings 32 KiB of A and 16 KiB
+// of B per CTA for eight MMAs: 48 bytes per MMA clock instead of 64, which is what the lone path from
+// L2 into an SM sustains. There is no second accumulator set; instead the two halves are published
+// and released separately: the epilogue drains half 0 while the last MMAs of half 1 still run, and the
+// next tile's MMAs into half 0 start while half 1 is being drained. With a long K loop the exposed
+// part of the epilogue is about one percent of a tile.
+constexpr int kTallBK = 64;
+constexpr int kTallStages = 4;
+constexpr int kTallABytes = 2 * kPairBM * kTallBK * 2;          // 256 rows
+constexpr int kTallBBytes = (kPairBN / 2) * kTallBK * 2;        // 128 of the 256 B rows
+constexpr int kTallStageBytes = kTallABytes + kTallBBytes;
+constexpr int kTallSmem = kTallStages * kTallStageBytes + 256 + 1024;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+gemm_pair_tall_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      float* __restrict__ C, int M, int N, int K, int64_t ldc, int tiles_m, int tiles_n, uint32_t* status,
+                      uint32_t idesc_extra) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = align_smem_1024(smem_raw);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + kTallStages * kTallABytes;
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + kTallStages * kTallStageBytes);  // used in the leader
+    uint64_t* bar_empty = bar_full + kTallStages;      // one per CTA
+    uint64_t* bar_acc_full = bar_empty + kTallStages;  // [half], one per CTA
+    uint64_t* bar_acc_empty = bar_acc_full + 2;        // [half], used in the leader
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_acc_empty + 2);
+    volatile uint32_t* abort_word = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();   // 0 = leader
+    const int pair = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+    const int num_tiles = tiles_m * tiles_n;
+    const int k_blocks = (K + kTallBK - 1) / kTallBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTallStages; ++s) {
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&bar_acc_full[a], 1);
+            mbar_init(&bar_acc_empty[a], 8);  // four epilogue warps in each CTA of the pair
+        }
+        *abort_word = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    cluster_sync_all();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_a);
+            tma_prefetch_desc(&tmap_b);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                int tm, tn;
+                pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+                const int row_a = tm * (4 * kPairBM) + static_cast<int>(rank) * (2 * kPairBM);
+                const int row_b = tn * kPairBN + static_cast<int>(rank) * (kPairBN / 2);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&bar_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full_addr = map_to_cta(smem_u32(&bar_full[stage]), 0);
+                    if (rank == 0) mbar_arrive_expect_tx(&bar_full[stage], 2 * kTallStageBytes);
+                    uint8_t* a_dst = smem_a + stage * kTallABytes;
+                    tma_load_2d_pair(a_dst, &tmap_a, full_addr, kb * kTallBK, row_a);
+                    tma_load_2d_pair(smem_b + stage * kTallBBytes, &tmap_b, full_addr, kb * kTallBK, row_b);
+                    tma_load_2d_pair(a_dst + kPairBM * 128, &tmap_a, full_addr, kb * kTallBK, row_a + kPairBM);
+                    if (++stage == kTallStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = make_idesc_f16_f32(2 * kPairBM, kPairBN, false, false) | idesc_extra;
+            const uint32_t desc_hi = smem_desc_hi_sw128(1024);
+            const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem_a), 16);
+            const uint32_t b_lo0 = smem_desc_lo(smem_u32(smem_b), 16);
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t tile_phase = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                for (int kb = 0; ok && kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&bar_full[stage], phase, abort_word, kDevTimeoutMma)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (kTallABytes >> 4);
+                    const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (kTallBBytes >> 4);
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        if (kb == 0) {   // the epilogue of the previous tile has drained this half
+                            if (!mbar_wait(&bar_acc_empty[half], tile_phase ^ 1u, abort_word, kDevTimeoutMma)) {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                        }
+                        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(half * kPairBN);
+                        const uint32_t a_half = a_lo + static_cast<uint32_t>(half * ((kPairBM * 128) >> 4));
+#pragma unroll
+                        for (int k = 0; k < kTallBK / 16; ++k)
+                            umma_f16_ss_pair(d_tmem, smem_desc_join(a_half + static_cast<uint32_t>(k * 2), desc_hi),
+                                             smem_desc_join(b_lo + static_cast<uint32_t>(k * 2), desc_hi), idesc, (kb | k) != 0);
+                        if (kb == k_blocks - 1) {
+                            umma_commit_pair(smem_u32(&bar_acc_full[half]));
+                            umma_commit_pair(map_to_cta(smem_u32(&bar_acc_full[half]), 1));
+                        }
+                    }
+                    if (!ok) break;
+                    umma_commit_pair(smem_u32(&bar_empty[stage]));
+                    umma_commit_pair(map_to_cta(smem_u32(&bar_empty[stage]), 1));
+                    if (++stage == kTallStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                tile_phase ^= 1u;
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue (both CTAs): TMEM -> registers -> global, one half at a time ----------------
+        const int quarter = warp & 3;
+        uint32_t tile_phase = 0;
+        bool ok = true;
+        const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
+        for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+            int tm, tn;
+            pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const int col0 = tn * kPairBN;
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+                if (!mbar_wait_warp(&bar_acc_full[half], tile_phase, abort_word, kDevTimeoutEpilogue)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const int row = tm * (4 * kPairBM) + static_cast<int>(rank) * (2 * kPairBM) + half * kPairBM + quarter * 32 + lane;
+                float* crow = C + static_cast<int64_t>(row) * ldc;
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(half * kPairBN);
+#pragma unroll 1
+                for (int c = 0; c < kPairBN / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_x32(taddr + static_cast<uint32_t>(c * 32), r);
+                    tmem_ld_wait();
+                    const int col = col0 + c * 32;
+                    if (row < M) {
+                        if (vec_ok && col + 32 <= N) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                       __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                                __stcs(reinterpret_cast<float4*>(crow + col) + j, v);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col + j < N) crow[col + j] = __uint_as_float(r[j]);
+                        }
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bar_acc_empty[half]), 0));
+            }
+            tile_phase ^= 1u;
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before_sync();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+    if (threadIdx.x == 0 && *abort_word != 0) atomicMax(status, *abort_word);
+}
+
+int launch_gemm_pair_tall(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int M, int N, int K, int64_t ldc,
+                          const DeviceInfo* dev, cudaStream_t stream, uint32_t idesc_extra) {
+    static bool configured[64] = {};
+    if (!configured[dev->device]) {
+        TCB_CUDA(cudaFuncSetAttribute(gemm_pair_tall_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTallSmem));
+        configured[dev->device] = true;
+    }
+    const int tiles_m = (M + 4 * kPairBM - 1) / (4 * kPairBM);
+    const int tiles_n = (N + kPairBN - 1) / kPairBN;
+    const int tiles = tiles_m * tiles_n;
+    const int max_pairs = dev->sm_count / 2;
+    const int pairs = tiles < max_pairs ? tiles : max_pairs;
+    gemm_pair_tall_kernel<<<2 * pairs, kPairThreads, kTallSmem, stream>>>(ta, tb, C, M, N, K, ldc, tiles_m, tiles_n,
+                                                                         dev->status_word, idesc_extra);
+    TCB_CUDA(cudaGetLastError());
+    return TC_OK;
+}
+
 int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int M, int N, int K, int64_t ldc,
                      const DeviceInfo* dev, cudaStream_t stream, uint32_t idesc_extra) {
     static bool configured[64] = {};
