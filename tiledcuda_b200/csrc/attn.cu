@@ -286,6 +286,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 for (int i = 0; i < 64; ++i)
                     if (i >= n_valid) s[i] = __float_as_uint(masked);
             }
+            // Exponentials are taken against the reference maximum m_used of the previous half blocks while the
+            // row extreme of this half block is still being reduced: the two are independent instruction
+            // streams (special-function unit against the ALU), and the reference only has to be replaced when
+            // some row outgrew it by 2^8, which after the first few half blocks is rare. When that happens
+            // the accumulator is rescaled and the exponentials are taken again from the scores, which are
+            // still in registers; the result is the same as reducing first.
+            uint32_t pk[32];
+            float sum0, sum1, sum2, sum3;
+            auto exponentials = [&](float neg_m) {
+                sum0 = sum1 = sum2 = sum3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float xa = fmaf(__uint_as_float(s[2 * i]), sc, neg_m);
+                    const float xb = fmaf(__uint_as_float(s[2 * i + 1]), sc, neg_m);
+                    const float xc = fmaf(__uint_as_float(s[2 * i + 2]), sc, neg_m);
+                    const float xd = fmaf(__uint_as_float(s[2 * i + 3]), sc, neg_m);
+                    const float a = fast_exp2(xa);
+                    const float b = (kFaPolyEvery == 2) ? poly_exp2(xb) : fast_exp2(xb);
+                    const float c2 = fast_exp2(xc);
+                    const float d2 = (kFaPolyEvery == 2 || kFaPolyEvery == 4) ? poly_exp2(xd) : fast_exp2(xd);
+                    sum0 += a;
+                    sum1 += b;
+                    sum2 += c2;
+                    sum3 += d2;
+                    pk[i] = pack_half2(a, b);
+                    pk[i + 1] = pack_half2(c2, d2);
+                }
+            };
+            if (g != 0) exponentials(-m_used);
             // row maximum of scale * s: the extreme of the raw scores times the scale (three-input max / min)
             float e0 = __uint_as_float(s[0]), e1 = __uint_as_float(s[1]), e2 = __uint_as_float(s[2]), e3 = __uint_as_float(s[3]);
             if (sc >= 0.f) {
@@ -314,7 +343,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             const float mx = e0 * sc;
             if (g == 0) m_used = fmaxf(mx, -1e30f);   // finite even for a row that sees no KV row at all
             // the accumulator is rescaled only when some row of the warp outgrew its reference maximum by 2^8
-            if (__any_sync(0xffffffffu, mx > m_used + kFaRescaleThreshold)) {
+            const bool outgrown = __any_sync(0xffffffffu, mx > m_used + kFaRescaleThreshold);
+            if (outgrown) {
                 float factor = 1.f;
                 if (mx > m_used + kFaRescaleThreshold) {
                     factor = fast_exp2(m_used - mx);
@@ -338,28 +368,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     tmem_st_x16(o_addr + static_cast<uint32_t>(c * 16), r);
                 }
             }
-            // exponentials, row sum, fp16 P written over the first 32 score columns. One exponential in
-            // kFaPolyEvery may be evaluated on the FMA pipe (poly_exp2) instead of the special-function unit.
-            const float neg_m = -m_used;
-            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                const float xa = fmaf(__uint_as_float(s[2 * i]), sc, neg_m);
-                const float xb = fmaf(__uint_as_float(s[2 * i + 1]), sc, neg_m);
-                const float xc = fmaf(__uint_as_float(s[2 * i + 2]), sc, neg_m);
-                const float xd = fmaf(__uint_as_float(s[2 * i + 3]), sc, neg_m);
-                const float a = fast_exp2(xa);
-                const float b = (kFaPolyEvery == 2) ? poly_exp2(xb) : fast_exp2(xb);
-                const float c2 = fast_exp2(xc);
-                const float d2 = (kFaPolyEvery == 2 || kFaPolyEvery == 4) ? poly_exp2(xd) : fast_exp2(xd);
-                sum0 += a;
-                sum1 += b;
-                sum2 += c2;
-                sum3 += d2;
-                s[i] = pack_half2(a, b);
-                s[i + 1] = pack_half2(c2, d2);
-            }
-            tmem_st_x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+            if (g == 0 || outgrown) exponentials(-m_used);
+            tmem_st_x32(s_addr, pk);
             l_sum += (sum0 + sum1) + (sum2 + sum3);
             tmem_st_wait();
             tc_fence_before_sync();
