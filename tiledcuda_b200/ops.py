@@ -15,8 +15,24 @@ import torch
 from . import _lib
 
 
+import contextlib
+
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_NO_GUARD = contextlib.nullcontext()
+
+
 def _stream() -> ctypes.c_void_p:
+    """The current CUDA stream of the current device as a raw handle."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _on(device: torch.device):
+    """Context that makes `device` current for the call; free when it already is (the usual case)."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(device)
 
 
 def _ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
@@ -52,7 +68,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> None:
         raise ValueError(f"shape mismatch: a {tuple(a.shape)}, b {tuple(b.shape)}, c {tuple(c.shape)}")
     lib = _lib.load()
     fn_name = "tc_gemm_bf16_f32" if in_dtype == torch.bfloat16 else "tc_gemm_f16_f32"
-    with torch.cuda.device(a.device):
+    with _on(a.device):
         _lib.check(
             fn_name,
             getattr(lib, fn_name)(_ptr(a), _ptr(b), _ptr(c), m, n, k, a.stride(0), b.stride(0), c.stride(0), _stream()),
@@ -76,7 +92,7 @@ def gemm_host(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, workspace: torc
     if kb != k or tuple(c.shape) != (m, n):
         raise ValueError(f"shape mismatch: a {tuple(a.shape)}, b {tuple(b.shape)}, c {tuple(c.shape)}")
     lib = _lib.load()
-    with torch.cuda.device(workspace.device):
+    with _on(workspace.device):
         _lib.check(
             "tc_gemm_f16_f32_host",
             lib.tc_gemm_f16_f32_host(_ptr(a), _ptr(b), _ptr(c), m, n, k, _ptr(workspace),
@@ -107,7 +123,7 @@ def back2back_gemm(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, e: torch.T
     if a.dim() == 3 and not (b.shape[0] == d.shape[0] == e.shape[0] == batch):
         raise ValueError("batch sizes differ")
     lib = _lib.load()
-    with torch.cuda.device(a.device):
+    with _on(a.device):
         _lib.check("tc_b2b_gemm_f16", lib.tc_b2b_gemm_f16(_ptr(a), _ptr(b), _ptr(d), _ptr(e), m, n, k, p, batch, _stream()))
 
 
@@ -156,7 +172,7 @@ def flash_attn(
     if scale is None:
         scale = 1.0 / math.sqrt(d)
     lib = _lib.load()
-    with torch.cuda.device(q.device):
+    with _on(q.device):
         if causal or seq_major:
             _lib.check(
                 "tc_flash_attn_fwd_ex_f16",
@@ -231,7 +247,7 @@ def lstm_cell(
     if h_out.data_ptr() == h_prev.data_ptr():
         raise ValueError("h_out must not alias h_prev")
     lib = _lib.load()
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         _lib.check(
             "tc_lstm_cell_f16",
             lib.tc_lstm_cell_f16(_ptr(w), _ptr(u), _ptr(bias), _ptr(x), _ptr(h_prev), _ptr(c_prev), _ptr(h_out),
@@ -273,7 +289,7 @@ def lstm_chain(
     if tuple(c0.shape) != (batch, hidden) or tuple(c_out.shape) != (batch, hidden):
         raise ValueError("c0 and c_out must be [batch, hidden]")
     lib = _lib.load()
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         if workspace is None:
             _lib.check(
                 "tc_lstm_chain_f16",
@@ -332,7 +348,7 @@ def scatter_nd(data: torch.Tensor, indices: torch.Tensor, updates: torch.Tensor)
     """
     dims, n, k = _scatter_args(data, indices, updates)
     lib = _lib.load()
-    with torch.cuda.device(data.device):
+    with _on(data.device):
         _lib.check(
             "tc_scatter_nd",
             lib.tc_scatter_nd(_ptr(data), _ptr(updates), _ptr(indices), int(indices.dtype == torch.int64), dims,
@@ -350,7 +366,7 @@ def scatter_nd_add(data: torch.Tensor, indices: torch.Tensor, updates: torch.Ten
         raise TypeError(f"scatter_nd_add supports {sorted(str(t) for t in _SCATTER_ADD_TYPES)}, got {data.dtype}")
     dims, n, k = _scatter_args(data, indices, updates)
     lib = _lib.load()
-    with torch.cuda.device(data.device):
+    with _on(data.device):
         _lib.check(
             "tc_scatter_nd_add",
             lib.tc_scatter_nd_add(_ptr(data), _ptr(updates), _ptr(indices), int(indices.dtype == torch.int64), dims,
