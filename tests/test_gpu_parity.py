@@ -31,6 +31,8 @@ def assert_close(out, ref, max_abs=oracle.MAX_ABS_TOL, rel_fro=oracle.REL_FRO_TO
         (1024, 1024, 1024),                      # configuration C1
         (1024, 1024, 2048), (2048, 2048, 2048),
         (2304, 2304, 64), (2250, 2300, 136), (4100, 2310, 328),  # enough 256x256 tiles for the CTA-pair kernel, ragged edges
+        (128, 19200, 256), (100, 19210, 264),    # one row tile, very wide: the lone 128x256 tiles
+        (300, 520, 4096), (1536, 1536, 1536),    # few pair tiles with a long K loop
     ],
 )
 def test_gemm_matches_oracle(cuda_ops, clean_status, m, n, k):

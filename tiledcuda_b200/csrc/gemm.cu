@@ -245,10 +245,20 @@ int launch_gemm_pair_tall(const CUtensorMap& ta, const CUtensorMap& tb, float* C
 int gemm_f16_f32_on(const DeviceInfo* dev, const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K,
                     int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t stream, bool bf16) {
     const uint32_t extra = bf16 ? kIdescBf16Inputs : 0u;
+    // Tile choice by a small cost model: waves over the machine times the tensor-pipe cycles one K step of 16
+    // costs in that tile (measured: 128 for a 256x256 pair tile; about 160 for a lone 128x256 tile and 128 for a
+    // lone 128x128 tile, both held back by shared-memory bandwidth, which the TMA writes and the MMA operand
+    // reads share), plus the exposed epilogue of the last wave.
+    const int64_t k16 = (K + 15) / 16;
+    const int64_t pairs = dev->sm_count / 2;
     const int64_t tiles_pair = ((M + 255) / 256) * ((N + 255) / 256);
-    const bool use_pair = tiles_pair >= dev->sm_count / 2;
     const int64_t tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
-    const bool use128 = !use_pair && ((N <= 128) || (tiles256 < dev->sm_count));
+    const int64_t tiles128 = ((M + 127) / 128) * ((N + 127) / 128);
+    const int64_t cost_pair = ((tiles_pair + pairs - 1) / pairs) * (128 * k16) + 1500;
+    const int64_t cost_256 = ((tiles256 + dev->sm_count - 1) / dev->sm_count) * (160 * k16) + 1500;
+    const int64_t cost_128 = ((tiles128 + dev->sm_count - 1) / dev->sm_count) * (128 * k16) + 800;
+    const bool use_pair = N > 128 && M > 128 && cost_pair <= cost_256 && cost_pair <= cost_128;
+    const bool use128 = !use_pair && (N <= 128 || cost_128 <= cost_256);
     const uint32_t bn = (use128 || use_pair) ? 128u : 256u;
     CUtensorMap ta, tb;
     {

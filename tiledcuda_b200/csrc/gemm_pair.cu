@@ -14,6 +14,9 @@
 // All waits are bounded; the two CTAs meet at a cluster barrier before either frees TMEM or exits.
 //
 // Stands in for the same reference code as gemm.cu (examples/cpp/01_gemm/02_gemm_all_mem/gemm.hpp:92-155).
+#include <stdlib.h>
+#include <string.h>
+
 #include "host.h"
 #include "sm100.cuh"
 
@@ -27,7 +30,8 @@ constexpr int kPairThreads = 192;
 constexpr int kPairABytes = kPairBM * kPairBK * 2;
 constexpr int kPairBBytes = (kPairBN / 2) * kPairBK * 2;
 constexpr int kPairStageBytes = kPairABytes + kPairBBytes;
-constexpr int kPairSmem = kPairStages * kPairStageBytes + 256 + 1024;
+constexpr int kPairStoreBytes = 4 * 2 * 4096;   // epilogue staging: per warp two 32-row x 128-byte boxes for TMA stores
+constexpr int kPairSmem = kPairStages * kPairStageBytes + kPairStoreBytes + 256 + 1024;
 constexpr int kPairGroupM = 8;    // pair-tiles (256 rows each) per rasterisation group
 
 __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -40,15 +44,66 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tile
     tn = in_group / rows;
 }
 
+// Tensor map of C for the TMA-store epilogue; *use_tma = 0 (and a zeroed map) when C or its row stride is not
+// 16-byte granular, in which case the kernels store from registers.
+static int pair_output_map(CUtensorMap* tc, int* use_tma, const float* C, int M, int N, int64_t ldc) {
+    memset(tc, 0, sizeof(*tc));
+    *use_tma = ((ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15u) == 0) ? 1 : 0;
+    if (const char* e = getenv("TC_GEMM_STORE"))   // "direct": stores from registers (tuning aid)
+        if (e[0] == 'd') *use_tma = 0;
+    if (!*use_tma) return TC_OK;
+    return encode_tmap_f32_sw128(tc, C, static_cast<uint64_t>(N), static_cast<uint64_t>(M), static_cast<uint64_t>(ldc) * 4, 32, 32);
+}
+
+// Drains the 32 rows x 256 columns of an accumulator that one epilogue warp owns (TMEM lanes of its quarter)
+// to C. With a tensor map for C the rows go through shared memory in 32 x 32 boxes (128-byte swizzle, the
+// layout the map expects) and leave as TMA stores of whole 128-byte lines, which the memory system takes
+// far better than 16-byte pieces of 32 different rows per instruction; the bulk-store groups belong to
+// lane 0, which also makes sure a staging box has been read out before it is overwritten. TMA clips boxes
+// at the edges of C. Without a map (C or ldc not 16-byte granular) each thread stores its own row.
+__device__ __forceinline__ void store_accumulator_rows(uint32_t taddr, float* __restrict__ C, const CUtensorMap* tmap_c,
+                                                       uint8_t* stage, int& buf, int row0, int col0, int M, int N,
+                                                       int64_t ldc, bool use_tma, int lane) {
+    const int row = row0 + lane;
+    float* crow = C + static_cast<int64_t>(row) * ldc;
+#pragma unroll 1
+    for (int c = 0; c < kPairBN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_x32(taddr + static_cast<uint32_t>(c * 32), r);
+        tmem_ld_wait();
+        const int col = col0 + c * 32;
+        if (use_tma) {
+            if (lane == 0) tma_store_wait_read<1>();   // the box written two chunks ago has left shared memory
+            __syncwarp();
+            uint8_t* box = stage + buf * 4096 + lane * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<uint4*>(box + ((j ^ (lane & 7)) << 4)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                if (row0 < M && col < N) tma_store_2d(tmap_c, stage + buf * 4096, col, row0);
+                tma_store_commit();
+            }
+            buf ^= 1;
+        } else if (row < M) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col + j < N) crow[col + j] = __uint_as_float(r[j]);
+        }
+    }
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 float* __restrict__ C, int M, int N, int K, int64_t ldc, int tiles_m, int tiles_n, uint32_t* status,
-                 uint32_t idesc_extra) {
+                 const __grid_constant__ CUtensorMap tmap_c, float* __restrict__ C, int M, int N, int K, int64_t ldc,
+                 int tiles_m, int tiles_n, uint32_t* status, uint32_t idesc_extra, int use_tma_store) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align_smem_1024(smem_raw);
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + kPairStages * kPairABytes;
-    uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);  // used in the leader
+    uint8_t* smem_store = smem + kPairStages * kPairStageBytes;   // 1024-byte aligned
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem_store + kPairStoreBytes);  // used in the leader
     uint64_t* bar_empty = bar_full + kPairStages;      // one per CTA
     uint64_t* bar_acc_full = bar_empty + kPairStages;  // one per CTA
     uint64_t* bar_acc_empty = bar_acc_full + 2;        // used in the leader
@@ -58,7 +113,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();   // 0 = leader
-    const uint32_t peer = rank ^ 1u;
     const int pair = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
     const int num_tiles = tiles_m * tiles_n;
@@ -169,41 +223,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         __syncwarp();
     } else {
-        // ---------------- epilogue (both CTAs): TMEM -> registers -> global ----------------
+        // ---------------- epilogue (both CTAs): TMEM -> registers -> (shared -> TMA store | global) ----------------
         const int quarter = warp & 3;
         int acc = 0;
         uint32_t acc_phase = 0;
-        const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
+        int buf = 0;
+        uint8_t* stage = smem_store + quarter * 8192;
+        const bool use_tma = use_tma_store != 0;
+        if (use_tma && lane == 0) tma_prefetch_desc(&tmap_c);
         for (int tile = pair; tile < num_tiles; tile += num_pairs) {
             int tm, tn;
             pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
             if (!mbar_wait_warp(&bar_acc_full[acc], acc_phase, abort_word, kDevTimeoutEpilogue)) break;
             tc_fence_after_sync();
-            const int row = tm * (2 * kPairBM) + static_cast<int>(rank) * kPairBM + quarter * 32 + lane;
-            const int col0 = tn * kPairBN;
-            float* crow = C + static_cast<int64_t>(row) * ldc;
+            const int row0 = tm * (2 * kPairBM) + static_cast<int>(rank) * kPairBM + quarter * 32;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * kPairBN);
-#pragma unroll 1
-            for (int c = 0; c < kPairBN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_x32(taddr + static_cast<uint32_t>(c * 32), r);
-                tmem_ld_wait();
-                const int col = col0 + c * 32;
-                if (row < M) {
-                    if (vec_ok && col + 32 <= N) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                            __stcs(reinterpret_cast<float4*>(crow + col) + j, v);
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col + j < N) crow[col + j] = __uint_as_float(r[j]);
-                    }
-                }
-            }
+            store_accumulator_rows(taddr, C, &tmap_c, stage, buf, row0, tn * kPairBN, M, N, ldc, use_tma, lane);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bar_acc_empty[acc]), 0));
@@ -212,6 +247,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 acc_phase ^= 1u;
             }
         }
+        if (use_tma && lane == 0) tma_store_wait<0>();   // all boxes written before the CTA may exit
     }
 
     // ---------------- teardown: neither CTA frees TMEM or exits while its peer may still touch it ----------------
@@ -237,17 +273,18 @@ constexpr int kTallStages = 4;
 constexpr int kTallABytes = 2 * kPairBM * kTallBK * 2;          // 256 rows
 constexpr int kTallBBytes = (kPairBN / 2) * kTallBK * 2;        // 128 of the 256 B rows
 constexpr int kTallStageBytes = kTallABytes + kTallBBytes;
-constexpr int kTallSmem = kTallStages * kTallStageBytes + 256 + 1024;
+constexpr int kTallSmem = kTallStages * kTallStageBytes + kPairStoreBytes + 256 + 1024;
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_pair_tall_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                      float* __restrict__ C, int M, int N, int K, int64_t ldc, int tiles_m, int tiles_n, uint32_t* status,
-                      uint32_t idesc_extra) {
+                      const __grid_constant__ CUtensorMap tmap_c, float* __restrict__ C, int M, int N, int K, int64_t ldc,
+                      int tiles_m, int tiles_n, uint32_t* status, uint32_t idesc_extra, int use_tma_store) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align_smem_1024(smem_raw);
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + kTallStages * kTallABytes;
-    uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + kTallStages * kTallStageBytes);  // used in the leader
+    uint8_t* smem_store = smem + kTallStages * kTallStageBytes;   // 1024-byte aligned
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem_store + kPairStoreBytes);  // used in the leader
     uint64_t* bar_empty = bar_full + kTallStages;      // one per CTA
     uint64_t* bar_acc_full = bar_empty + kTallStages;  // [half], one per CTA
     uint64_t* bar_acc_empty = bar_acc_full + 2;        // [half], used in the leader
@@ -368,15 +405,17 @@ gemm_pair_tall_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
         __syncwarp();
     } else {
-        // ---------------- epilogue (both CTAs): TMEM -> registers -> global, one half at a time ----------------
+        // ---------------- epilogue (both CTAs), one accumulator half at a time ----------------
         const int quarter = warp & 3;
         uint32_t tile_phase = 0;
         bool ok = true;
-        const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
+        int buf = 0;
+        uint8_t* stage = smem_store + quarter * 8192;
+        const bool use_tma = use_tma_store != 0;
+        if (use_tma && lane == 0) tma_prefetch_desc(&tmap_c);
         for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
             int tm, tn;
             pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
-            const int col0 = tn * kPairBN;
 #pragma unroll 1
             for (int half = 0; half < 2; ++half) {
                 if (!mbar_wait_warp(&bar_acc_full[half], tile_phase, abort_word, kDevTimeoutEpilogue)) {
@@ -384,36 +423,16 @@ gemm_pair_tall_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                     break;
                 }
                 tc_fence_after_sync();
-                const int row = tm * (4 * kPairBM) + static_cast<int>(rank) * (2 * kPairBM) + half * kPairBM + quarter * 32 + lane;
-                float* crow = C + static_cast<int64_t>(row) * ldc;
+                const int row0 = tm * (4 * kPairBM) + static_cast<int>(rank) * (2 * kPairBM) + half * kPairBM + quarter * 32;
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(half * kPairBN);
-#pragma unroll 1
-                for (int c = 0; c < kPairBN / 32; ++c) {
-                    uint32_t r[32];
-                    tmem_ld_x32(taddr + static_cast<uint32_t>(c * 32), r);
-                    tmem_ld_wait();
-                    const int col = col0 + c * 32;
-                    if (row < M) {
-                        if (vec_ok && col + 32 <= N) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                                       __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                                __stcs(reinterpret_cast<float4*>(crow + col) + j, v);
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col + j < N) crow[col + j] = __uint_as_float(r[j]);
-                        }
-                    }
-                }
+                store_accumulator_rows(taddr, C, &tmap_c, stage, buf, row0, tn * kPairBN, M, N, ldc, use_tma, lane);
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bar_acc_empty[half]), 0));
             }
             tile_phase ^= 1u;
         }
+        if (use_tma && lane == 0) tma_store_wait<0>();
     }
 
     // ---------------- teardown ----------------
@@ -428,6 +447,9 @@ gemm_pair_tall_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 
 int launch_gemm_pair_tall(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int M, int N, int K, int64_t ldc,
                           const DeviceInfo* dev, cudaStream_t stream, uint32_t idesc_extra) {
+    CUtensorMap tc;
+    int use_tma = 0;
+    if (int rc = pair_output_map(&tc, &use_tma, C, M, N, ldc)) return rc;
     static bool configured[64] = {};
     if (!configured[dev->device]) {
         TCB_CUDA(cudaFuncSetAttribute(gemm_pair_tall_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTallSmem));
@@ -438,14 +460,17 @@ int launch_gemm_pair_tall(const CUtensorMap& ta, const CUtensorMap& tb, float* C
     const int tiles = tiles_m * tiles_n;
     const int max_pairs = dev->sm_count / 2;
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
-    gemm_pair_tall_kernel<<<2 * pairs, kPairThreads, kTallSmem, stream>>>(ta, tb, C, M, N, K, ldc, tiles_m, tiles_n,
-                                                                         dev->status_word, idesc_extra);
+    gemm_pair_tall_kernel<<<2 * pairs, kPairThreads, kTallSmem, stream>>>(ta, tb, tc, C, M, N, K, ldc, tiles_m, tiles_n,
+                                                                         dev->status_word, idesc_extra, use_tma);
     TCB_CUDA(cudaGetLastError());
     return TC_OK;
 }
 
 int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int M, int N, int K, int64_t ldc,
                      const DeviceInfo* dev, cudaStream_t stream, uint32_t idesc_extra) {
+    CUtensorMap tc;
+    int use_tma = 0;
+    if (int rc = pair_output_map(&tc, &use_tma, C, M, N, ldc)) return rc;
     static bool configured[64] = {};
     if (!configured[dev->device]) {
         TCB_CUDA(cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem));
@@ -456,8 +481,8 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int
     const int tiles = tiles_m * tiles_n;
     const int max_pairs = dev->sm_count / 2;
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
-    gemm_pair_kernel<<<2 * pairs, kPairThreads, kPairSmem, stream>>>(ta, tb, C, M, N, K, ldc, tiles_m, tiles_n,
-                                                                    dev->status_word, idesc_extra);
+    gemm_pair_kernel<<<2 * pairs, kPairThreads, kPairSmem, stream>>>(ta, tb, tc, C, M, N, K, ldc, tiles_m, tiles_n,
+                                                                    dev->status_word, idesc_extra, use_tma);
     TCB_CUDA(cudaGetLastError());
     return TC_OK;
 }

@@ -90,6 +90,23 @@ int encode_tmap_f16_sw128(CUtensorMap* out, const void* base, int rank, const ui
     return TC_OK;
 }
 
+int encode_tmap_f32_sw128(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint64_t row_stride_bytes,
+                          uint32_t box_cols, uint32_t box_rows) {
+    if (int rc = load_encode()) return rc;
+    const cuuint64_t gdim[2] = {cols, rows};
+    const cuuint64_t gstride[1] = {row_stride_bytes};
+    const cuuint32_t bdim[2] = {box_cols, box_rows};
+    const cuuint32_t estride[2] = {1, 1};
+    CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), gdim, gstride, bdim, estride,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(TC_ERR_CUDA, "cuTensorMapEncodeTiled (fp32 output) failed with CUresult %d (%llu x %llu, stride %llu)",
+                    static_cast<int>(r), (unsigned long long)cols, (unsigned long long)rows,
+                    (unsigned long long)row_stride_bytes);
+    return TC_OK;
+}
+
 }  // namespace tcb
 
 extern "C" {

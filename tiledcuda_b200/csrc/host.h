@@ -45,6 +45,10 @@ int current_device(const DeviceInfo** out);
 int encode_tmap_f16_sw128(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                           const uint64_t* strides_bytes, const uint32_t* box, bool bf16 = false);
 
+// Tiled fp32 2-D map with 128-byte swizzle (rows of 32 floats), for TMA stores of accumulator tiles.
+int encode_tmap_f32_sw128(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint64_t row_stride_bytes,
+                          uint32_t box_cols, uint32_t box_rows);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace tcb
