@@ -274,12 +274,11 @@ int gemm_f16_f32_on(const DeviceInfo* dev, const void* A, const void* B, float* 
         if (int rc = encode_tmap_f16_sw128(&tb, B, 2, dims, strides, box, bf16)) return rc;
     }
     if (use_pair) {
-        // Operands far larger than L2 take 512x256 tiles, which fetch a quarter fewer operand bytes per FLOP
-        // (measured at 16384^3: 1369 against 1262 TFLOP/s; at 8192^3 the two are equal, below that the
-        // coarser tiles lose to wave quantisation).
-        const int64_t operand_bytes = (M + N) * K * 2;
+        // Long K loops over many tiles take 512x256 tiles, which fetch a quarter fewer operand bytes per FLOP and
+        // expose only about one percent of a tile's epilogue (measured: 8192^3 1484 against 1456 TFLOP/s, 16384^3
+        // 1446 against 1262; equal at 4096^3 and 6144^3; with K = 2048 the square tiles win, 1326 against 1284).
         const int64_t tiles_tall = ((M + 511) / 512) * ((N + 255) / 256);
-        bool use_tall = operand_bytes >= (512ll << 20) && K >= 2048 && tiles_tall >= 2 * (dev->sm_count / 2);
+        bool use_tall = K >= 4096 && tiles_tall >= 4 * pairs;
         if (const char* force = getenv("TC_GEMM_PAIR_TILE")) {   // "tall" or "square": overrides the choice (tuning aid)
             if (force[0] == 't') use_tall = true;
             if (force[0] == 's') use_tall = false;
