@@ -17,6 +17,7 @@
 
 #include "host.h"
 #include "sm100.cuh"
+#include "epilogue.cuh"
 
 namespace tcb {
 
@@ -31,7 +32,7 @@ struct GemmSmem {
     static constexpr int kBBytes = BN * kGemmBK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarBytes = 256;
-    static constexpr int kTotal = STAGES * kStageBytes + kBarBytes + 1024;  // + slack for 1024-B alignment
+    static constexpr int kTotal = STAGES * kStageBytes + kStoreStageBytes + kBarBytes + 1024;  // + slack for 1024-B alignment
 };
 
 __device__ __forceinline__ void gemm_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -47,14 +48,15 @@ __device__ __forceinline__ void gemm_tile_coords(int tile, int tiles_m, int tile
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    float* __restrict__ C, int M, int N, int K, int64_t ldc, int tiles_m, int tiles_n,
-                    uint32_t* status, uint32_t idesc_extra) {
+                    const __grid_constant__ CUtensorMap tmap_c, float* __restrict__ C, int M, int N, int K, int64_t ldc,
+                    int tiles_m, int tiles_n, uint32_t* status, uint32_t idesc_extra, int use_tma_store) {
     using S = GemmSmem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align_smem_1024(smem_raw);
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + STAGES * S::kABytes;
-    uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes);
+    uint8_t* smem_store = smem + STAGES * S::kStageBytes;   // 1024-byte aligned
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem_store + kStoreStageBytes);
     uint64_t* bar_empty = bar_full + STAGES;
     uint64_t* bar_acc_full = bar_empty + STAGES;
     uint64_t* bar_acc_empty = bar_acc_full + 2;
@@ -157,41 +159,21 @@ gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         __syncwarp();
     } else {
-        // ---------------- epilogue: TMEM -> registers -> global ----------------
+        // ---------------- epilogue: TMEM -> registers -> (shared -> TMA store | global) ----------------
         const int quarter = warp & 3;  // TMEM lane quarter this warp may read
         int acc = 0;
         uint32_t acc_phase = 0;
-        const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
+        int buf = 0;
+        uint8_t* stage = smem_store + quarter * 8192;
+        const bool use_tma = use_tma_store != 0;
+        if (use_tma && lane == 0) tma_prefetch_desc(&tmap_c);
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
             int tm, tn;
             gemm_tile_coords(tile, tiles_m, tiles_n, tm, tn);
             if (!mbar_wait_warp(&bar_acc_full[acc], acc_phase, abort_word, kDevTimeoutEpilogue)) break;
             tc_fence_after_sync();
-            const int row = tm * kGemmBM + quarter * 32 + lane;
-            const int col0 = tn * BN;
-            float* crow = C + static_cast<int64_t>(row) * ldc;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_x32(taddr + static_cast<uint32_t>(c * 32), r);
-                tmem_ld_wait();
-                const int col = col0 + c * 32;
-                if (row < M) {
-                    if (vec_ok && col + 32 <= N) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                            __stcs(reinterpret_cast<float4*>(crow + col) + j, v);
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col + j < N) crow[col + j] = __uint_as_float(r[j]);
-                    }
-                }
-            }
+            store_accumulator_rows<BN>(taddr, C, &tmap_c, stage, buf, tm * kGemmBM + quarter * 32, tn * BN, M, N, ldc, use_tma, lane);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_acc_empty[acc]);
@@ -200,6 +182,7 @@ gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 acc_phase ^= 1u;
             }
         }
+        if (use_tma && lane == 0) tma_store_wait<0>();   // all boxes written before the CTA may exit
     }
 
     // ---------------- teardown ----------------
@@ -226,7 +209,11 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, float* C, i
     const int tiles_n = (N + BN - 1) / BN;
     const int tiles = tiles_m * tiles_n;
     const int grid = tiles < dev->sm_count ? tiles : dev->sm_count;
-    kernel<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, C, M, N, K, ldc, tiles_m, tiles_n, dev->status_word, idesc_extra);
+    CUtensorMap tc;
+    int use_tma = 0;
+    if (int rc = output_store_map(&tc, &use_tma, C, M, N, ldc)) return rc;
+    kernel<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, tc, C, M, N, K, ldc, tiles_m, tiles_n, dev->status_word, idesc_extra,
+                                                      use_tma);
     TCB_CUDA(cudaGetLastError());
     return TC_OK;
 }
