@@ -52,6 +52,19 @@ int tc_gemm_f16_f32(const void* A, const void* B, void* C, int64_t M, int64_t N,
 int tc_gemm_bf16_f32(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
                      int64_t ldb, int64_t ldc, tc_stream_t stream);
 
+/* Which tile shape tc_gemm_f16_f32 / tc_gemm_bf16_f32 run a problem with on a device of sm_count SMs (148 on
+ * B200): a pure function of its arguments, usable without a GPU. Returns one of TC_GEMM_TILE_* (or a negative
+ * status). It stands where the reference picks tile shapes by compiling and timing candidate kernels at run time
+ * (examples/python/gemm/main.py:37-70 with compile.py:83-127); here the table is fixed ahead of time from
+ * measurements. */
+enum {
+    TC_GEMM_TILE_128x128 = 0,       /* lone CTA, 128x128x64, six stages */
+    TC_GEMM_TILE_128x256 = 1,       /* lone CTA, 128x256x64, four stages */
+    TC_GEMM_TILE_PAIR_256x256 = 2,  /* CTA pair, tcgen05.mma.cta_group::2, double-buffered accumulators */
+    TC_GEMM_TILE_PAIR_512x256 = 3   /* CTA pair, two accumulator halves per CTA */
+};
+int tc_gemm_tile_plan(int64_t M, int64_t N, int64_t K, int sm_count);
+
 /* The same GEMM with HOST operands and result (contiguous: lda = ldb = K, ldc = N), for callers whose data
  * lives in host memory, as the reference's Python examples' does before `.cuda()`
  * (examples/python/gemm/main.py:47-52). Uploads, products and downloads are pipelined block by block over

@@ -20,7 +20,7 @@ def declared_symbols():
 
 def test_header_declares_the_expected_entry_points():
     names = declared_symbols()
-    for want in ("tc_gemm_f16_f32", "tc_gemm_bf16_f32", "tc_gemm_f16_f32_host", "tc_lstm_chain_ws_f16", "tc_lstm_chain_static_f16", "tc_b2b_gemm_f16", "tc_flash_attn_fwd_f16", "tc_flash_attn_fwd_ex_f16", "tc_scatter_nd_add", "tc_lstm_cell_f16",
+    for want in ("tc_gemm_f16_f32", "tc_gemm_bf16_f32", "tc_gemm_f16_f32_host", "tc_gemm_tile_plan", "tc_lstm_chain_ws_f16", "tc_lstm_chain_static_f16", "tc_b2b_gemm_f16", "tc_flash_attn_fwd_f16", "tc_flash_attn_fwd_ex_f16", "tc_scatter_nd_add", "tc_lstm_cell_f16",
                  "tc_lstm_chain_f16", "tc_scatter_nd", "tc_last_error", "tc_device_status", "tc_version"):
         assert want in names
 
@@ -86,3 +86,18 @@ def test_check_raises_with_the_library_message():
     with pytest.raises(_lib.TiledCudaError) as ei:
         _lib.check("tc_gemm_f16_f32", rc)
     assert ei.value.status == -1 and "null" in str(ei.value)
+
+
+def test_gemm_tile_plan_is_a_pure_function_and_parity_shapes_cover_every_tile():
+    """tc_gemm_tile_plan needs no GPU. The headline size takes the tall pair tiles, mid sizes the square pair
+    tiles, small ones lone CTAs; and the GEMM shapes of the GPU parity suite reach all four kernels."""
+    lib = _lib.load()
+    plan = lambda m, n, k: lib.tc_gemm_tile_plan(m, n, k, 148)
+    assert plan(8192, 8192, 8192) == 3 and plan(16384, 16384, 16384) == 3
+    assert plan(4096, 4096, 4096) == 2 and plan(2048, 2048, 2048) == 2 and plan(8192, 8192, 2048) == 2
+    assert plan(1024, 1024, 1024) == 0 and plan(16, 16, 16) == 0 and plan(100000, 64, 512) == 0
+    assert plan(128, 19200, 256) == 1
+    assert lib.tc_gemm_tile_plan(0, 8, 8, 148) == -1 and lib.tc_gemm_tile_plan(8, 8, 8, 0) == -1
+    from tests.test_gpu_parity import GEMM_SHAPES
+    kinds = {plan(*shape) for shape in GEMM_SHAPES} | {plan(16384 + 328, 16384 - 56, 8192)}  # + the tall-tile test
+    assert kinds == {0, 1, 2, 3}

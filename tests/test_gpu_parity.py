@@ -21,9 +21,7 @@ def assert_close(out, ref, max_abs=oracle.MAX_ABS_TOL, rel_fro=oracle.REL_FRO_TO
 
 
 # ------------------------------------------------------------------------------------------- GEMM
-@pytest.mark.parametrize(
-    "m,n,k",
-    [
+GEMM_SHAPES = [
         (16, 16, 16), (64, 128, 128),            # single-warp shapes of tests/cpp/cell/test_single_wmma.cu:190-195
         (128, 128, 64), (128, 256, 64),          # one tile of each kernel variant
         (32, 64, 32), (96, 48, 128), (128, 128, 128),  # shapes from tests/cpp/cell/test_gemm.cu:306-351
@@ -33,8 +31,10 @@ def assert_close(out, ref, max_abs=oracle.MAX_ABS_TOL, rel_fro=oracle.REL_FRO_TO
         (2304, 2304, 64), (2250, 2300, 136), (4100, 2310, 328),  # enough 256x256 tiles for the CTA-pair kernel, ragged edges
         (128, 19200, 256), (100, 19210, 264),    # one row tile, very wide: the lone 128x256 tiles
         (300, 520, 4096), (1536, 1536, 1536),    # few pair tiles with a long K loop
-    ],
-)
+    ]
+
+
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
 def test_gemm_matches_oracle(cuda_ops, clean_status, m, n, k):
     a, b = oracle.gemm_inputs(m, n, k)
     c = torch.full((m, n), float("nan"), device=DEV)

@@ -13,6 +13,7 @@
 // Stands in for the reference's `gemm` (examples/cpp/01_gemm/02_gemm_all_mem/gemm.hpp:92-155: cp.async
 // -> swizzled smem -> ldmatrix -> mma.sync, single stage) and cell::compute::gemm
 // (include/cell/compute/gemm.hpp:19-88).
+#include <stdint.h>
 #include <stdlib.h>
 
 #include "host.h"
@@ -226,27 +227,43 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int
 int launch_gemm_pair_tall(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int M, int N, int K, int64_t ldc,
                           const DeviceInfo* dev, cudaStream_t stream, uint32_t idesc_extra);
 
+// Tile shape for a problem on a device with sm_count SMs: TC_GEMM_TILE_* of the public header.
+// A small cost model: waves over the machine times the tensor-pipe cycles one K step of 16 costs in that tile
+// (measured: 128 for a 256x256 pair tile; about 160 for a lone 128x256 tile and 128 for a lone 128x128 tile, both
+// held back by shared-memory bandwidth, which the TMA writes and the MMA operand reads share), plus the exposed
+// epilogue of the last wave. Long K loops over many tiles take 512x256 pair tiles, which fetch a quarter fewer
+// operand bytes per FLOP and expose only about one percent of a tile's epilogue (measured: 8192^3 1484 against
+// 1456 TFLOP/s, 16384^3 1446 against 1262; equal at 4096^3 and 6144^3; with K = 2048 the square tiles win, 1326
+// against 1284).
+int gemm_tile_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
+    const int64_t k16 = (K + 15) / 16;
+    const int64_t pairs = sm_count / 2;
+    const int64_t tiles_pair = ((M + 255) / 256) * ((N + 255) / 256);
+    const int64_t tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
+    const int64_t tiles128 = ((M + 127) / 128) * ((N + 127) / 128);
+    const int64_t cost_pair = pairs > 0 ? ((tiles_pair + pairs - 1) / pairs) * (128 * k16) + 1500 : INT64_MAX;
+    const int64_t cost_256 = ((tiles256 + sm_count - 1) / sm_count) * (160 * k16) + 1500;
+    const int64_t cost_128 = ((tiles128 + sm_count - 1) / sm_count) * (128 * k16) + 800;
+    if (N > 128 && M > 128 && cost_pair <= cost_256 && cost_pair <= cost_128) {
+        const int64_t tiles_tall = ((M + 511) / 512) * ((N + 255) / 256);
+        return (K >= 4096 && tiles_tall >= 4 * pairs) ? TC_GEMM_TILE_PAIR_512x256 : TC_GEMM_TILE_PAIR_256x256;
+    }
+    return (N <= 128 || cost_128 <= cost_256) ? TC_GEMM_TILE_128x128 : TC_GEMM_TILE_128x256;
+}
+
 // The dispatch of tc_gemm_f16_f32 for a caller that brings its own device record (and therefore its own
 // status word) instead of the lazily allocated per-device one. Arguments are trusted: the caller has
 // validated them. Used by entry points that must not allocate.
 int gemm_f16_f32_on(const DeviceInfo* dev, const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K,
                     int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t stream, bool bf16) {
     const uint32_t extra = bf16 ? kIdescBf16Inputs : 0u;
-    // Tile choice by a small cost model: waves over the machine times the tensor-pipe cycles one K step of 16
-    // costs in that tile (measured: 128 for a 256x256 pair tile; about 160 for a lone 128x256 tile and 128 for a
-    // lone 128x128 tile, both held back by shared-memory bandwidth, which the TMA writes and the MMA operand
-    // reads share), plus the exposed epilogue of the last wave.
-    const int64_t k16 = (K + 15) / 16;
-    const int64_t pairs = dev->sm_count / 2;
-    const int64_t tiles_pair = ((M + 255) / 256) * ((N + 255) / 256);
-    const int64_t tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
-    const int64_t tiles128 = ((M + 127) / 128) * ((N + 127) / 128);
-    const int64_t cost_pair = ((tiles_pair + pairs - 1) / pairs) * (128 * k16) + 1500;
-    const int64_t cost_256 = ((tiles256 + dev->sm_count - 1) / dev->sm_count) * (160 * k16) + 1500;
-    const int64_t cost_128 = ((tiles128 + dev->sm_count - 1) / dev->sm_count) * (128 * k16) + 800;
-    const bool use_pair = N > 128 && M > 128 && cost_pair <= cost_256 && cost_pair <= cost_128;
-    const bool use128 = !use_pair && (N <= 128 || cost_128 <= cost_256);
-    const uint32_t bn = (use128 || use_pair) ? 128u : 256u;
+    int plan = gemm_tile_plan(M, N, K, dev->sm_count);
+    if (const char* force = getenv("TC_GEMM_PAIR_TILE")) {   // "tall" or "square": overrides the pair tile (tuning aid)
+        if (plan == TC_GEMM_TILE_PAIR_256x256 && force[0] == 't') plan = TC_GEMM_TILE_PAIR_512x256;
+        if (plan == TC_GEMM_TILE_PAIR_512x256 && force[0] == 's') plan = TC_GEMM_TILE_PAIR_256x256;
+    }
+    const bool use_pair = plan == TC_GEMM_TILE_PAIR_256x256 || plan == TC_GEMM_TILE_PAIR_512x256;
+    const uint32_t bn = plan == TC_GEMM_TILE_128x256 ? 256u : 128u;
     CUtensorMap ta, tb;
     {
         const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
@@ -260,20 +277,9 @@ int gemm_f16_f32_on(const DeviceInfo* dev, const void* A, const void* B, float* 
         const uint32_t box[2] = {kGemmBK, bn};
         if (int rc = encode_tmap_f16_sw128(&tb, B, 2, dims, strides, box, bf16)) return rc;
     }
-    if (use_pair) {
-        // Long K loops over many tiles take 512x256 tiles, which fetch a quarter fewer operand bytes per FLOP and
-        // expose only about one percent of a tile's epilogue (measured: 8192^3 1484 against 1456 TFLOP/s, 16384^3
-        // 1446 against 1262; equal at 4096^3 and 6144^3; with K = 2048 the square tiles win, 1326 against 1284).
-        const int64_t tiles_tall = ((M + 511) / 512) * ((N + 255) / 256);
-        bool use_tall = K >= 4096 && tiles_tall >= 4 * pairs;
-        if (const char* force = getenv("TC_GEMM_PAIR_TILE")) {   // "tall" or "square": overrides the choice (tuning aid)
-            if (force[0] == 't') use_tall = true;
-            if (force[0] == 's') use_tall = false;
-        }
-        if (use_tall) return launch_gemm_pair_tall(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
-        return launch_gemm_pair(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
-    }
-    if (use128) return launch_gemm<128, 6>(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
+    if (plan == TC_GEMM_TILE_PAIR_512x256) return launch_gemm_pair_tall(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
+    if (use_pair) return launch_gemm_pair(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
+    if (plan == TC_GEMM_TILE_128x128) return launch_gemm<128, 6>(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
     return launch_gemm<256, 4>(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
 }
 
@@ -306,4 +312,10 @@ extern "C" int tc_gemm_f16_f32(const void* A, const void* B, void* C, int64_t M,
 extern "C" int tc_gemm_bf16_f32(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
                                 int64_t ldb, int64_t ldc, tc_stream_t stream) {
     return gemm_entry("gemm_bf16", true, A, B, C, M, N, K, lda, ldb, ldc, stream);
+}
+
+extern "C" int tc_gemm_tile_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
+    using namespace tcb;
+    TCB_REQUIRE(M > 0 && N > 0 && K > 0 && sm_count > 0, "gemm_tile_plan: M, N, K and sm_count must be positive");
+    return gemm_tile_plan(M, N, K, sm_count);
 }
