@@ -37,6 +37,31 @@ __global__ void k_roundtrip(const T* in, T* out) {
     store(s, gout);
 }
 
+// global -> shared -> global through a GTileIterator, chunk by chunk: the shapes of the reference's swizzled-load
+// tests (tests/cpp/cell/test_swizzled_copy.cu:399-449). Each chunk goes into a shared operand tile (128-byte
+// swizzle or interleaved core matrices) and back out to the same chunk of the output.
+template <typename GLayout, typename ChunkShape, typename SLayout, bool kSwizzled>
+__global__ void k_chunked_roundtrip(const __half* in, __half* out) {
+    extern __shared__ uint8_t raw[];
+    using Global = GlobalTile<__half, GLayout>;
+    using GIter = GTileIterator<Global, ChunkShape>;
+    using Shared = SharedTile<__half, SLayout, kSwizzled>;
+    Shared s(reinterpret_cast<__half*>(align1024(raw)));
+    GIter gin(in), gout(out);
+    copy::GlobalToSharedLoader<Shared, WarpLayout> load;
+    copy::SharedToGlobalStorer<Shared, WarpLayout> store;
+    constexpr int kChunks = GIter::sc0 * GIter::sc1;
+    for (int i = 0; i < kChunks; ++i) {
+        auto src = gin(i);
+        auto dst = gout(i);
+        load(src, s);
+        __copy_async();
+        __syncthreads();
+        store(s, dst);
+        __syncthreads();
+    }
+}
+
 // ------------------------------------------------------------------------------------ tile GEMM
 // C[M,N] = A[M,K] B[K,N] with A row-major, B column-major, fp32 C, K walked in chunks of TK.
 template <int M, int N, int K, int TK, bool kSwizzled>
@@ -203,7 +228,7 @@ static int set_smem(Kernel k, int bytes) {
 
 // Shapes of the reference's test_gemm.cu:306-351 (M, N, K, chunk K), each with and without swizzle where the
 // chunk is a whole number of 64-element swizzle rows.
-extern "C" int tcx_gemm_case_count() { return 22; }
+extern "C" int tcx_gemm_case_count() { return 43; }
 extern "C" int tcx_tile_gemm(int id, const __half* A, const __half* B, float* C, int* status, int* m, int* n, int* k) {
     switch (id) {
         GEMM_CASE(0, 16, 16, 16, 16, false)
@@ -228,6 +253,28 @@ extern "C" int tcx_tile_gemm(int id, const __half* A, const __half* B, float* C,
         GEMM_CASE(19, 64, 256, 256, 128, true)
         GEMM_CASE(20, 128, 80, 192, 64, true)
         GEMM_CASE(21, 48, 112, 96, 16, false)
+        // the remaining (M, N, K, K chunk) shapes of tests/cpp/cell/test_gemm.cu:312-350
+        GEMM_CASE(22, 32, 16, 16, 16, true)
+        GEMM_CASE(23, 16, 32, 16, 16, false)
+        GEMM_CASE(24, 16, 16, 32, 16, true)
+        GEMM_CASE(25, 16, 16, 32, 32, false)
+        GEMM_CASE(26, 16, 32, 32, 16, true)
+        GEMM_CASE(27, 32, 32, 32, 16, false)
+        GEMM_CASE(28, 32, 32, 32, 32, true)
+        GEMM_CASE(29, 32, 64, 32, 16, false)
+        GEMM_CASE(30, 32, 64, 32, 32, true)
+        GEMM_CASE(31, 32, 64, 64, 16, false)
+        GEMM_CASE(32, 32, 64, 64, 32, true)
+        GEMM_CASE(33, 32, 16, 32, 16, false)
+        GEMM_CASE(34, 64, 32, 32, 16, true)
+        GEMM_CASE(35, 64, 32, 128, 32, false)
+        GEMM_CASE(36, 32, 32, 64, 32, true)
+        GEMM_CASE(37, 64, 32, 64, 32, false)
+        GEMM_CASE(38, 32, 32, 128, 64, true)
+        GEMM_CASE(39, 64, 64, 128, 32, false)
+        GEMM_CASE(40, 64, 64, 128, 128, true)
+        GEMM_CASE(41, 128, 128, 64, 32, false)
+        GEMM_CASE(42, 64, 128, 128, 64, true)
         default: return -1;
     }
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
@@ -257,6 +304,68 @@ extern "C" int tcx_roundtrip(int id, const void* in, void* out, int* rows, int* 
         RT_CASE(9, float, tl::RowMajor, 16, 16, false)
         RT_CASE(10, float, tl::RowMajor, 64, 128, false)
         RT_CASE(11, float, tl::ColMajor, 128, 32, false)
+        default: return -1;
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+#define CRT_CASE(id, LAYOUT, R, C, SR, SC, CM)                                                      \
+    case id: {                                                                                    \
+        if (swizzled) {                                                                           \
+            auto kern = k_chunked_roundtrip<LAYOUT<R, C>, TileShape<SR, SC>, LAYOUT<SR, SC>, true>;                                    \
+            if (set_smem(kern, 140 * 1024)) return -3;                                            \
+            kern<<<1, 128, 140 * 1024>>>(in, out);                                                \
+        } else {                                                                                  \
+            auto kern = k_chunked_roundtrip<LAYOUT<R, C>, TileShape<SR, SC>, LAYOUT<SR, SC>, false>;                                   \
+            if (set_smem(kern, 140 * 1024)) return -3;                                            \
+            kern<<<1, 128, 140 * 1024>>>(in, out);                                                \
+        }                                                                                         \
+        *rows = R; *cols = C; *col_major = CM;                                                    \
+        break;                                                                                    \
+    }
+
+// 24 row-major and 13 column-major configurations: (rows, cols, shared chunk extent) of
+// tests/cpp/cell/test_swizzled_copy.cu:400-429 and :433-449.
+extern "C" int tcx_chunked_roundtrip_case_count() { return 37; }
+extern "C" int tcx_chunked_roundtrip(int id, int swizzled, const __half* in, __half* out, int* rows, int* cols, int* col_major) {
+    switch (id) {
+        CRT_CASE(0, tl::RowMajor, 16, 16, 16, 16, 0)
+        CRT_CASE(1, tl::RowMajor, 16, 32, 16, 32, 0)
+        CRT_CASE(2, tl::RowMajor, 16, 32, 16, 32, 0)
+        CRT_CASE(3, tl::RowMajor, 32, 32, 32, 32, 0)
+        CRT_CASE(4, tl::RowMajor, 32, 64, 32, 32, 0)
+        CRT_CASE(5, tl::RowMajor, 16, 64, 16, 32, 0)
+        CRT_CASE(6, tl::RowMajor, 16, 128, 16, 64, 0)
+        CRT_CASE(7, tl::RowMajor, 32, 32, 32, 32, 0)
+        CRT_CASE(8, tl::RowMajor, 64, 64, 64, 64, 0)
+        CRT_CASE(9, tl::RowMajor, 32, 64, 32, 32, 0)
+        CRT_CASE(10, tl::RowMajor, 32, 128, 32, 64, 0)
+        CRT_CASE(11, tl::RowMajor, 64, 128, 64, 64, 0)
+        CRT_CASE(12, tl::RowMajor, 64, 256, 64, 128, 0)
+        CRT_CASE(13, tl::RowMajor, 32, 32, 32, 32, 0)
+        CRT_CASE(14, tl::RowMajor, 32, 32, 32, 32, 0)
+        CRT_CASE(15, tl::RowMajor, 32, 64, 32, 32, 0)
+        CRT_CASE(16, tl::RowMajor, 128, 256, 128, 128, 0)
+        CRT_CASE(17, tl::RowMajor, 64, 64, 64, 64, 0)
+        CRT_CASE(18, tl::RowMajor, 64, 128, 64, 64, 0)
+        CRT_CASE(19, tl::RowMajor, 64, 128, 64, 128, 0)
+        CRT_CASE(20, tl::RowMajor, 64, 256, 64, 128, 0)
+        CRT_CASE(21, tl::RowMajor, 128, 64, 128, 64, 0)
+        CRT_CASE(22, tl::RowMajor, 256, 512, 256, 256, 0)
+        CRT_CASE(23, tl::RowMajor, 128, 256, 128, 128, 0)
+        CRT_CASE(24, tl::ColMajor, 16, 16, 16, 16, 1)
+        CRT_CASE(25, tl::ColMajor, 32, 16, 32, 16, 1)
+        CRT_CASE(26, tl::ColMajor, 32, 16, 32, 16, 1)
+        CRT_CASE(27, tl::ColMajor, 32, 32, 16, 32, 1)
+        CRT_CASE(28, tl::ColMajor, 64, 64, 32, 64, 1)
+        CRT_CASE(29, tl::ColMajor, 128, 64, 64, 64, 1)
+        CRT_CASE(30, tl::ColMajor, 128, 32, 64, 32, 1)
+        CRT_CASE(31, tl::ColMajor, 256, 128, 64, 128, 1)
+        CRT_CASE(32, tl::ColMajor, 32, 32, 32, 32, 1)
+        CRT_CASE(33, tl::ColMajor, 128, 32, 64, 32, 1)
+        CRT_CASE(34, tl::ColMajor, 128, 64, 64, 64, 1)
+        CRT_CASE(35, tl::ColMajor, 256, 128, 128, 128, 1)
+        CRT_CASE(36, tl::ColMajor, 128, 128, 64, 128, 1)
         default: return -1;
     }
     return cudaGetLastError() == cudaSuccess ? 0 : -2;

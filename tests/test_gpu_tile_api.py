@@ -29,7 +29,7 @@ def _p(t):
 
 
 def test_case_counts(lib):
-    assert lib.tcx_gemm_case_count() == 22 and lib.tcx_roundtrip_case_count() == 12
+    assert lib.tcx_gemm_case_count() == 43 and lib.tcx_roundtrip_case_count() == 12
 
 
 @pytest.mark.parametrize("case", range(12))
@@ -50,7 +50,25 @@ def test_global_shared_round_trip_is_exact(lib, case):
     assert torch.equal(out, ramp)
 
 
-@pytest.mark.parametrize("case", range(22))
+@pytest.mark.parametrize("swizzled", [1, 0])
+@pytest.mark.parametrize("case", range(37))
+def test_chunked_round_trip_reference_shapes(lib, case, swizzled):
+    """The 24 row-major and 13 column-major shapes of the reference's swizzled-load tests
+    (tests/cpp/cell/test_swizzled_copy.cu:399-449), walked chunk by chunk with a GTileIterator through a shared
+    operand tile in both operand layouts; the output must reproduce the `i % 2048` ramp exactly."""
+    assert lib.tcx_chunked_roundtrip_case_count() == 37
+    rows, cols, cm = (ctypes.c_int() for _ in range(3))
+    n_max = 256 * 512
+    ramp = (torch.arange(n_max, device=DEV) % 2048).to(torch.float16)
+    out = torch.full((n_max,), -1, dtype=torch.float16, device=DEV)
+    assert lib.tcx_chunked_roundtrip(case, swizzled, _p(ramp), _p(out), ctypes.byref(rows), ctypes.byref(cols), ctypes.byref(cm)) == 0
+    torch.cuda.synchronize()
+    n = rows.value * cols.value
+    assert torch.equal(out[:n], ramp[:n])
+    assert (out[n:] == -1).all()
+
+
+@pytest.mark.parametrize("case", range(43))
 def test_tile_gemm_matches_oracle(lib, case):
     a_buf = torch.zeros(128 * 512, dtype=torch.float16, device=DEV)
     b_buf = torch.zeros(256 * 512, dtype=torch.float16, device=DEV)
