@@ -183,6 +183,118 @@ __global__ void k_tile_b2b(const __half* dA, const __half* dB, const __half* dD,
     if (threadIdx.x < 32) copy::TmemAllocator::free(accS.address(), tmem_alloc_columns(N + P));
 }
 
+// ------------------------------------------------------------------------------------ tile flash attention
+// O[M,P] = softmax(Q K^T) V for one tile of M <= 128 query rows, KV walked in blocks of BN with two GTileIterators,
+// written with the tile vocabulary only and following the reference's recurrence statement for statement
+// (tests/python/test_flash_attn.py:27-75; examples/cpp/03_flash_attention/flash_attn.hpp): per block
+//   cur_max = rowmax(S); E = exp(S - cur_max); cur_sum = rowsum(E); new_max = max(cur_max, prev_max);
+//   renorm_prev = exp(prev_max - new_max); renorm_cur = exp(cur_max - new_max);
+//   new_sum = renorm_prev prev_sum + renorm_cur cur_sum; O = (O prev_sum renorm_prev + renorm_cur (E V)) / new_sum.
+// Q is row-major [M,K], K the column-major [K,N] operand (stored [N,K]), V the column-major [N,P] operand (stored
+// [P,N]), as the reference's kernel takes them. fp32 statistics; E is rounded to fp16 for the second product.
+template <int M, int N, int K, int P, int BN>
+__global__ void k_tile_flash_attn(const __half* dQ, const __half* dK, const __half* dV, float* dO, int* status) {
+    extern __shared__ uint8_t raw[];
+    using GlobalQ = GlobalTile<__half, tl::RowMajor<M, K>>;
+    using GlobalK = GlobalTile<__half, tl::ColMajor<K, N>>;
+    using GlobalV = GlobalTile<__half, tl::ColMajor<N, P>>;
+    using GlobalO = GlobalTile<float, tl::RowMajor<M, P>>;
+    using IterK = GTileIterator<GlobalK, TileShape<K, BN>>;
+    using IterV = GTileIterator<GlobalV, TileShape<BN, P>>;
+    using SharedQ = SharedTile<__half, tl::RowMajor<M, K>, true>;
+    using SharedK = SharedTile<__half, tl::ColMajor<K, BN>, true>;
+    using SharedV = SharedTile<__half, tl::ColMajor<BN, P>, true>;
+    using SharedE = SharedTile<__half, tl::RowMajor<128, BN>, true>;
+    using AccS = TmemTile<float, tl::RowMajor<128, BN>>;
+    using AccO = TmemTile<float, tl::RowMajor<128, P>>;
+    using RegS = RowFragment<float, BN>;
+    using RegO = RowFragment<float, P>;
+    using Val = RowScalar<float>;
+
+    uint8_t* smem = align1024(raw);
+    SharedQ sQ(reinterpret_cast<__half*>(smem));
+    SharedK sK(reinterpret_cast<__half*>(smem + 32 * 1024));
+    SharedV sV(reinterpret_cast<__half*>(smem + 64 * 1024));
+    SharedE sE(reinterpret_cast<__half*>(smem + 96 * 1024));
+    uint64_t* bar_mem = reinterpret_cast<uint64_t*>(smem + 128 * 1024);
+    uint32_t* slot = reinterpret_cast<uint32_t*>(bar_mem + 1);
+
+    MmaBarrier bar(bar_mem);
+    if (threadIdx.x == 0) bar.init();
+    if (threadIdx.x < 32) copy::TmemAllocator::alloc(slot, tmem_alloc_columns(BN + P));
+    __syncthreads();
+    AccS accS(*slot);
+    AccO accEV(*slot + BN);
+
+    GlobalQ gQ(dQ);
+    IterK gKs(dK);
+    IterV gVs(dV);
+    copy::GlobalToSharedLoader<SharedQ, WarpLayout>{}(gQ, sQ);
+
+    RegS rS, rE;
+    RegO rO, rEV;
+    Val prev_max, prev_sum, cur_max, cur_sum, new_max, new_sum, renorm_prev, renorm_cur, tmp;
+    rO.clear();
+    prev_max.clear();
+    prev_sum.clear();
+    bool ok = true;
+
+    for (int j = 0; j < N / BN; ++j) {
+        auto gK = gKs(j);
+        auto gV = gVs(j);
+        copy::GlobalToSharedLoader<SharedK, WarpLayout>{}(gK, sK);
+        copy::GlobalToSharedLoader<SharedV, WarpLayout>{}(gV, sV);
+        __copy_async();
+        __syncthreads();
+
+        compute::gemm(sQ, sK, accS, false);
+        if (threadIdx.x == 0) bar.commit();
+        ok = bar.wait() && ok;
+        copy::TmemToRegLoader<AccS, RegS>{}(accS, rS);
+
+        compute::MaxReduce<RegS>{}(rS, cur_max);
+        copy::copy(rS, rE);
+        compute::BroadcastSub<Val, RegS>{}(cur_max, rE);
+        compute::RegTileExp<RegS>{}(rE, rE);
+        compute::SumReduce<RegS>{}(rE, cur_sum);
+
+        compute::RegTileMax<Val>{}(cur_max, prev_max, new_max);
+        compute::RegTileSub<Val>{}(prev_max, new_max, renorm_prev);
+        compute::RegTileExp<Val>{}(renorm_prev, renorm_prev);
+        compute::RegTileSub<Val>{}(cur_max, new_max, renorm_cur);
+        compute::RegTileExp<Val>{}(renorm_cur, renorm_cur);
+        compute::RegTileMul<Val>{}(renorm_prev, prev_sum, tmp);          // renorm_prev * prev_sum
+        compute::RegTileMul<Val>{}(renorm_cur, cur_sum, new_sum);
+        compute::RegTileAdd<Val>{}(new_sum, tmp, new_sum);
+
+        copy::RegToSharedStorer<RegS, WarpLayout>{}(rE, sE);   // rounds to fp16, writes the operand layout
+        fence_async_proxy();
+        __syncthreads();
+        compute::gemm(sE, sV, accEV, false);
+        if (threadIdx.x == 0) bar.commit();
+        ok = bar.wait() && ok;
+        copy::TmemToRegLoader<AccO, RegO>{}(accEV, rEV);
+
+        compute::BroadcastMul<Val, RegO>{}(tmp, rO);             // O * prev_sum * renorm_prev
+        compute::BroadcastMul<Val, RegO>{}(renorm_cur, rEV);
+        compute::RegTileAdd<RegO>{}(rO, rEV, rO);
+        compute::BroadcastDiv<Val, RegO>{}(new_sum, rO);
+        copy::copy(new_sum, prev_sum);
+        copy::copy(new_max, prev_max);
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();   // sK, sV and sE are rewritten by the next block
+    }
+    if (ok) {
+        GlobalO gO(dO);
+        copy::RegToGlobalStorer<GlobalO, RegO, WarpLayout>{}(rO, gO);
+    } else if (threadIdx.x == 0) {
+        *status = 1;
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x < 32) copy::TmemAllocator::free(accS.address(), tmem_alloc_columns(BN + P));
+}
+
 // ------------------------------------------------------------------------------------ row operations
 // in [128, C] fp32 -> softmax rows, row max, row sum, (x - max) broadcast, exp, per-warp column sums.
 template <int C>
@@ -391,6 +503,31 @@ extern "C" int tcx_tile_b2b(int id, const __half* A, const __half* B, const __ha
         *m = 32; *n = 128; *k = 64; *p = 48;
     } else {
         return -1;
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+#define FA_CASE(id, M, N, K, P, BN)                                                       \
+    case id: {                                                                            \
+        auto kern = k_tile_flash_attn<M, N, K, P, BN>;                                    \
+        if (set_smem(kern, 130 * 1024 + 1024)) return -3;                                 \
+        kern<<<1, 128, 130 * 1024 + 1024>>>(Q, K_, V, O, status);                         \
+        *m = M; *n = N; *k = K; *p = P;                                                   \
+        break;                                                                            \
+    }
+
+// The first three are the shapes the reference's attention kernel is built for (src/kernels/flash_attn.cu:438-455).
+extern "C" int tcx_tile_flash_attn_case_count() { return 6; }
+extern "C" int tcx_tile_flash_attn(int id, const __half* Q, const __half* K_, const __half* V, float* O, int* status, int* m,
+                                   int* n, int* k, int* p) {
+    switch (id) {
+        FA_CASE(0, 64, 64, 128, 128, 64)
+        FA_CASE(1, 64, 128, 128, 128, 64)
+        FA_CASE(2, 64, 256, 128, 128, 64)
+        FA_CASE(3, 128, 512, 128, 128, 128)
+        FA_CASE(4, 128, 256, 64, 64, 64)
+        FA_CASE(5, 32, 128, 32, 48, 32)
+        default: return -1;
     }
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

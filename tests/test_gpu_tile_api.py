@@ -6,6 +6,7 @@ test_swizzled_copy.cu:399-499, test_softmax.cu:117-163); results are compared on
 import ctypes
 from pathlib import Path
 
+import numpy as np
 import pytest
 import torch
 
@@ -103,6 +104,37 @@ def test_tile_b2b_matches_oracle(lib, case):
     torch.cuda.synchronize()
     assert rc == 0 and status.item() == 0 and (m.value, n.value, k.value, p.value) == dims
     assert oracle.within_tolerance(e, oracle.back2back_gemm(a[0], b[0], d[0]))
+
+
+@pytest.mark.parametrize("case", range(6))
+def test_tile_flash_attention_matches_oracle(lib, case, golden_dir):
+    """Flash attention written with the tile vocabulary (GTileIterator over KV blocks, compute::gemm into TMEM,
+    MaxReduce / SumReduce / Broadcast* / RegTileExp for the reference's recurrence). Cases 0-2 are the reference's
+    three shapes on its own test inputs, checked against the output of its Python oracle as well."""
+    assert lib.tcx_tile_flash_attn_case_count() == 6
+    dims = [(64, 64, 128, 128), (64, 128, 128, 128), (64, 256, 128, 128), (128, 512, 128, 128), (128, 256, 64, 64),
+            (32, 128, 32, 48)][case]
+    M, N, K, P = dims
+    golden = None
+    if case < 3:
+        g = np.load(golden_dir / f"flash_attn_ref_n{N}.npz")
+        q, k, v = torch.from_numpy(g["q"]), torch.from_numpy(g["k_t"]).t().contiguous(), torch.from_numpy(g["v"])
+        golden = torch.from_numpy(g["o"])
+    else:
+        q4, k4, v4 = oracle.attention_inputs(1, 1, M, N, K, P, seed=300 + case)
+        q, k, v = q4[0, 0], (k4[0, 0].float() * 0.3).half(), v4[0, 0]
+    qd, kd, vtd = q.to(DEV).contiguous(), k.to(DEV).contiguous(), v.to(DEV).t().contiguous()
+    o = torch.full((M, P), float("nan"), device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    m, n, kk, p = (ctypes.c_int() for _ in range(4))
+    rc = lib.tcx_tile_flash_attn(case, _p(qd), _p(kd), _p(vtd), _p(o), _p(status), ctypes.byref(m), ctypes.byref(n),
+                                 ctypes.byref(kk), ctypes.byref(p))
+    torch.cuda.synchronize()
+    assert rc == 0 and status.item() == 0 and (m.value, n.value, kk.value, p.value) == dims
+    ref, _ = oracle.flash_attention(q, k, v, scale=1.0)
+    assert oracle.within_tolerance(o, ref)
+    if golden is not None:
+        assert oracle.max_abs_err(o, golden) <= 2e-2
 
 
 @pytest.mark.parametrize("cols", [16, 64, 128])
