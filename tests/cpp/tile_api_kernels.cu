@@ -401,7 +401,7 @@ extern "C" int tcx_tile_gemm(int id, const __half* A, const __half* B, float* C,
         break;                                                                            \
     }
 
-extern "C" int tcx_roundtrip_case_count() { return 12; }
+extern "C" int tcx_roundtrip_case_count() { return 42; }
 extern "C" int tcx_roundtrip(int id, const void* in, void* out, int* rows, int* cols, int* elem, int* col_major) {
     switch (id) {
         RT_CASE(0, __half, tl::RowMajor, 16, 16, false)
@@ -416,6 +416,37 @@ extern "C" int tcx_roundtrip(int id, const void* in, void* out, int* rows, int* 
         RT_CASE(9, float, tl::RowMajor, 16, 16, false)
         RT_CASE(10, float, tl::RowMajor, 64, 128, false)
         RT_CASE(11, float, tl::ColMajor, 128, 32, false)
+        // the shapes of the reference's global-to-shared load tests (tests/cpp/cell/test_g2s_load.cu:118-143)
+        RT_CASE(12, __half, tl::RowMajor, 16, 32, false)
+        RT_CASE(13, __half, tl::RowMajor, 16, 32, true)
+        RT_CASE(14, __half, tl::RowMajor, 32, 128, false)
+        RT_CASE(15, __half, tl::RowMajor, 32, 128, true)
+        RT_CASE(16, __half, tl::RowMajor, 192, 32, false)
+        RT_CASE(17, __half, tl::RowMajor, 192, 32, true)
+        RT_CASE(18, __half, tl::RowMajor, 64, 128, false)
+        RT_CASE(19, __half, tl::RowMajor, 64, 128, true)
+        RT_CASE(20, __half, tl::RowMajor, 96, 128, false)
+        RT_CASE(21, __half, tl::RowMajor, 96, 128, true)
+        RT_CASE(22, float, tl::RowMajor, 16, 16, false)
+        RT_CASE(23, float, tl::RowMajor, 32, 128, false)
+        RT_CASE(24, float, tl::RowMajor, 192, 32, false)
+        RT_CASE(25, float, tl::RowMajor, 64, 128, false)
+        RT_CASE(26, float, tl::RowMajor, 96, 128, false)
+        RT_CASE(27, __half, tl::ColMajor, 16, 16, false)
+        RT_CASE(28, __half, tl::ColMajor, 16, 16, true)
+        RT_CASE(29, __half, tl::ColMajor, 32, 128, false)
+        RT_CASE(30, __half, tl::ColMajor, 32, 128, true)
+        RT_CASE(31, __half, tl::ColMajor, 192, 32, false)
+        RT_CASE(32, __half, tl::ColMajor, 192, 32, true)
+        RT_CASE(33, __half, tl::ColMajor, 64, 128, false)
+        RT_CASE(34, __half, tl::ColMajor, 64, 128, true)
+        RT_CASE(35, __half, tl::ColMajor, 96, 128, false)
+        RT_CASE(36, __half, tl::ColMajor, 96, 128, true)
+        RT_CASE(37, float, tl::ColMajor, 16, 16, false)
+        RT_CASE(38, float, tl::ColMajor, 32, 128, false)
+        RT_CASE(39, float, tl::ColMajor, 192, 32, false)
+        RT_CASE(40, float, tl::ColMajor, 64, 128, false)
+        RT_CASE(41, float, tl::ColMajor, 96, 128, false)
         default: return -1;
     }
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
