@@ -34,12 +34,8 @@ constexpr int kFaTile = 128 * 128 * 2;
 constexpr int kFaChunk = 128 * 64 * 2;
 constexpr int kFaSmem = kFaTile * (2 + kFaStages) + 256 + 1024;
 constexpr float kFaRescaleThreshold = 8.0f;
-#ifndef TCB_FA_POLY_EVERY
-#define TCB_FA_POLY_EVERY 0
-#endif
-constexpr int kFaPolyEvery = TCB_FA_POLY_EVERY;   // 4: one exponential in four on the FMA pipe; 2: every other; 0: none.
-// Measured at s4096 d128: 0 -> 1068, 4 -> 1002, 2 -> 886 TFLOP/s, so the default keeps every exponential on the
-// special-function unit: the softmax warps are short of issue slots, not of ex2 throughput.
+// Evaluating part of the exponentials on the FMA pipe (a degree-3 polynomial, poly_exp2 in sm100.cuh) was measured
+// slower at every share tried (1/4: 1002 against 1068 TFLOP/s; 1/2: 886): all of them use the special-function unit.
 
 struct AttnParams {
     int seq_q;
@@ -293,19 +289,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             // the accumulator is rescaled and the exponentials are taken again from the scores, which are
             // still in registers; the result is the same as reducing first.
             uint32_t pk[32];
-            float sum0, sum1, sum2, sum3;
+            float sum0, sum1, sum2, sum3, r0, r1;
+            // x = scale * s - reference for all 64 scores, exp2(x) rounded to fp16 pairs, the partial sums, and (in
+            // the shadow of the exponentials, which leave most issue slots free) the largest x
             auto exponentials = [&](float neg_m) {
                 sum0 = sum1 = sum2 = sum3 = 0.f;
+                r0 = r1 = -INFINITY;
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     const float xa = fmaf(__uint_as_float(s[2 * i]), sc, neg_m);
                     const float xb = fmaf(__uint_as_float(s[2 * i + 1]), sc, neg_m);
                     const float xc = fmaf(__uint_as_float(s[2 * i + 2]), sc, neg_m);
                     const float xd = fmaf(__uint_as_float(s[2 * i + 3]), sc, neg_m);
+                    r0 = fmax3(r0, xa, xb);
+                    r1 = fmax3(r1, xc, xd);
                     const float a = fast_exp2(xa);
-                    const float b = (kFaPolyEvery == 2) ? poly_exp2(xb) : fast_exp2(xb);
+                    const float b = fast_exp2(xb);
                     const float c2 = fast_exp2(xc);
-                    const float d2 = (kFaPolyEvery == 2 || kFaPolyEvery == 4) ? poly_exp2(xd) : fast_exp2(xd);
+                    const float d2 = fast_exp2(xd);
                     sum0 += a;
                     sum1 += b;
                     sum2 += c2;
@@ -314,41 +315,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     pk[i + 1] = pack_half2(c2, d2);
                 }
             };
-            if (g != 0) exponentials(-m_used);
-            // row maximum of scale * s: the extreme of the raw scores times the scale (three-input max / min)
-            float e0 = __uint_as_float(s[0]), e1 = __uint_as_float(s[1]), e2 = __uint_as_float(s[2]), e3 = __uint_as_float(s[3]);
-            if (sc >= 0.f) {
-#pragma unroll
-                for (int i = 4; i < 60; i += 8) {
-                    e0 = fmax3(e0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
-                    e1 = fmax3(e1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
-                    e2 = fmax3(e2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
-                    e3 = fmax3(e3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
-                }
-                e0 = fmax3(e0, __uint_as_float(s[60]), __uint_as_float(s[61]));
-                e1 = fmax3(e1, __uint_as_float(s[62]), __uint_as_float(s[63]));
-                e0 = fmaxf(fmaxf(e0, e1), fmaxf(e2, e3));
+            float over;   // by how much the largest scaled score of this half block exceeds the reference
+            if (g == 0) {
+                exponentials(0.f);                            // first half block: only the maximum is used
+                m_used = fmaxf(fmaxf(r0, r1), -1e30f);        // finite even for a row that sees no KV row at all
+                exponentials(-m_used);
+                over = 0.f;
             } else {
-#pragma unroll
-                for (int i = 4; i < 60; i += 8) {
-                    e0 = fmin3(e0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
-                    e1 = fmin3(e1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
-                    e2 = fmin3(e2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
-                    e3 = fmin3(e3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
-                }
-                e0 = fmin3(e0, __uint_as_float(s[60]), __uint_as_float(s[61]));
-                e1 = fmin3(e1, __uint_as_float(s[62]), __uint_as_float(s[63]));
-                e0 = fminf(fminf(e0, e1), fminf(e2, e3));
+                exponentials(-m_used);
+                over = fmaxf(r0, r1);
             }
-            const float mx = e0 * sc;
-            if (g == 0) m_used = fmaxf(mx, -1e30f);   // finite even for a row that sees no KV row at all
             // the accumulator is rescaled only when some row of the warp outgrew its reference maximum by 2^8
-            const bool outgrown = __any_sync(0xffffffffu, mx > m_used + kFaRescaleThreshold);
+            const bool outgrown = __any_sync(0xffffffffu, over > kFaRescaleThreshold);
             if (outgrown) {
                 float factor = 1.f;
-                if (mx > m_used + kFaRescaleThreshold) {
-                    factor = fast_exp2(m_used - mx);
-                    m_used = mx;
+                if (over > kFaRescaleThreshold) {
+                    factor = fast_exp2(-over);
+                    m_used += over;
                 }
                 l_sum *= factor;
                 // O_t may still be the target of P_t(g-1) V(g-1): wait for it. Seeing s_full of half block g
@@ -368,7 +351,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     tmem_st_x16(o_addr + static_cast<uint32_t>(c * 16), r);
                 }
             }
-            if (g == 0 || outgrown) exponentials(-m_used);
+            if (outgrown) exponentials(-m_used);
             tmem_st_x32(s_addr, pk);
             l_sum += (sum0 + sum1) + (sum2 + sum3);
             tmem_st_wait();
