@@ -62,6 +62,26 @@ def test_new_ops_are_registered_and_match(ptc):
     ptc.lstm_cell(w.to(DEV), u.to(DEV), None, x[0].to(DEV), h0.to(DEV), c0.to(DEV), h1, c1)
 
 
+def test_extended_ops_through_the_dispatcher(ptc):
+    """Causal and sequence-major attention and the accumulating scatter as torch ops."""
+    q, k, v = oracle.attention_inputs(1, 2, 256, 256, 64)
+    o = torch.empty(1, 2, 256, 64, dtype=torch.float16, device=DEV)
+    ptc.flash_attn_ex(q.to(DEV), k.to(DEV), v.to(DEV), o, causal=True)
+    assert oracle.within_tolerance(o, oracle.flash_attention(q, k, v, causal=True)[0])
+    to_sm = lambda t: t.to(DEV).transpose(1, 2).contiguous()
+    o2 = torch.empty(1, 256, 2, 64, dtype=torch.float16, device=DEV)
+    ptc.flash_attn_ex(to_sm(q), to_sm(k), to_sm(v), o2, causal=True, seq_major=True)
+    assert torch.equal(o2.transpose(1, 2), o)
+
+    g = torch.Generator().manual_seed(5)
+    table = torch.randint(-8, 8, (300, 4), generator=g).float()
+    idx = torch.randint(0, 300, (1000, 1), generator=g)
+    upd = torch.randint(-4, 4, (1000, 4), generator=g).float()
+    dev = table.to(DEV)
+    ptc.scatter_nd_add(dev, idx.to(DEV), upd.to(DEV))
+    assert dev.cpu().numpy().tobytes() == oracle.scatter_nd_add(table.numpy(), idx.numpy(), upd.numpy()).tobytes()
+
+
 def test_errors_surface_as_runtime_errors(ptc):
     a = torch.zeros(128, 60, dtype=torch.float16, device=DEV)
     with pytest.raises(RuntimeError, match="multiple of 8"):

@@ -47,6 +47,30 @@ void scatter_nd_op(at::Tensor& data, const at::Tensor& updates, const at::Tensor
                                       static_cast<int>(data.element_size()), stream_of(data)));
 }
 
+// The accumulating form, which is what the reference's kernel does (src/kernels/scatter_nd.cu:44-47).
+void scatter_nd_add_op(at::Tensor& data, const at::Tensor& updates, const at::Tensor& indices) {
+    TORCH_CHECK(data.is_cuda() && updates.is_cuda() && indices.is_cuda(), "scatter_nd_add needs CUDA tensors");
+    TORCH_CHECK(data.is_contiguous() && updates.is_contiguous() && indices.is_contiguous(), "scatter_nd_add needs contiguous tensors");
+    TORCH_CHECK(updates.scalar_type() == data.scalar_type(), "updates and data must have the same dtype");
+    int elem_type = -1;
+    switch (data.scalar_type()) {
+        case at::kFloat: elem_type = 0; break;
+        case at::kHalf: elem_type = 1; break;
+        case at::kInt: elem_type = 2; break;
+        case at::kDouble: elem_type = 3; break;
+        default: TORCH_CHECK(false, "scatter_nd_add supports float32, float16, int32 and float64 tables");
+    }
+    const bool i64 = indices.scalar_type() == at::kLong;
+    TORCH_CHECK(i64 || indices.scalar_type() == at::kInt, "indices must be int32 or int64");
+    TORCH_CHECK(indices.dim() >= 1, "indices must have at least one dimension");
+    const int64_t k = indices.size(-1);
+    const int64_t n = k > 0 ? indices.numel() / k : 0;
+    std::vector<int64_t> dims(data.sizes().begin(), data.sizes().end());
+    c10::cuda::CUDAGuard guard(data.device());
+    check("scatter_nd_add", tc_scatter_nd_add(data.data_ptr(), updates.data_ptr(), indices.data_ptr(), i64 ? 1 : 0, dims.data(),
+                                              static_cast<int>(dims.size()), n, static_cast<int>(k), elem_type, stream_of(data)));
+}
+
 // Same signature as custom_flash_attention_op (include/kernels/flash_attn.hpp:35-37): flattened fp16
 // Q [m,k], K [n,k], V^T [p,n], O [m,p]; one head; no softmax scale.
 void flash_attention_fwd_op(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& V, at::Tensor& O, int64_t m,
@@ -78,6 +102,24 @@ void flash_attn_op(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& V
     c10::cuda::CUDAGuard guard(Q.device());
     check("flash_attn", tc_flash_attn_fwd_f16(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), nullptr, b, h, sq, skv, d, dv,
                                               static_cast<float>(scale), v_is_transposed ? 1 : 0, stream_of(Q)));
+}
+
+// flash_attn with a causal mask (bottom-right aligned) and / or [B,S,H,D] operands.
+void flash_attn_ex_op(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& V, at::Tensor& O, double scale, bool causal,
+                      bool seq_major) {
+    need(Q, "Q", at::kHalf);
+    need(K, "K", at::kHalf);
+    need(V, "V", at::kHalf);
+    need(O, "O", at::kHalf);
+    TORCH_CHECK(Q.dim() == 4 && K.dim() == 4 && V.dim() == 4 && O.dim() == 4, "flash_attn_ex: tensors must be 4-D");
+    const int sd = seq_major ? 1 : 2, hd = seq_major ? 2 : 1;
+    const int64_t b = Q.size(0), h = Q.size(hd), sq = Q.size(sd), d = Q.size(3), skv = K.size(sd), dv = V.size(3);
+    TORCH_CHECK(K.size(0) == b && K.size(hd) == h && K.size(3) == d, "flash_attn_ex: K shape mismatch");
+    TORCH_CHECK(V.size(0) == b && V.size(hd) == h && V.size(sd) == skv, "flash_attn_ex: V shape mismatch");
+    TORCH_CHECK(O.size(0) == b && O.size(hd) == h && O.size(sd) == sq && O.size(3) == dv, "flash_attn_ex: O shape mismatch");
+    c10::cuda::CUDAGuard guard(Q.device());
+    check("flash_attn_ex", tc_flash_attn_fwd_ex_f16(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), nullptr, b, h, sq, skv, d,
+                                                    dv, static_cast<float>(scale), 0, causal ? 1 : 0, seq_major ? 1 : 0, stream_of(Q)));
 }
 
 // C[M,N] fp32 = A[M,K] @ B[N,K]^T (B is the column-major operand of the reference's GEMM examples).
@@ -135,6 +177,8 @@ TORCH_LIBRARY(tiledcuda, m) {
     m.def("scatter_nd(Tensor(a!) data, Tensor updates, Tensor indices) -> ()");
     m.def("flash_attention_fwd(Tensor Q, Tensor K, Tensor V, Tensor(a!) O, int m, int n, int k, int p) -> ()");
     m.def("flash_attn(Tensor Q, Tensor K, Tensor V, Tensor(a!) O, float scale, bool v_is_transposed) -> ()");
+    m.def("flash_attn_ex(Tensor Q, Tensor K, Tensor V, Tensor(a!) O, float scale, bool causal, bool seq_major) -> ()");
+    m.def("scatter_nd_add(Tensor(a!) data, Tensor updates, Tensor indices) -> ()");
     m.def("gemm(Tensor A, Tensor B, Tensor(a!) C) -> ()");
     m.def("back2back_gemm(Tensor A, Tensor B, Tensor D, Tensor(a!) E) -> ()");
     m.def("lstm_cell(Tensor W, Tensor U, Tensor? bias, Tensor x, Tensor h_prev, Tensor c_prev, Tensor(a!) h_out, "
@@ -145,6 +189,8 @@ TORCH_LIBRARY_IMPL(tiledcuda, CUDA, m) {
     m.impl("scatter_nd", &scatter_nd_op);
     m.impl("flash_attention_fwd", &flash_attention_fwd_op);
     m.impl("flash_attn", &flash_attn_op);
+    m.impl("flash_attn_ex", &flash_attn_ex_op);
+    m.impl("scatter_nd_add", &scatter_nd_add_op);
     m.impl("gemm", &gemm_op);
     m.impl("back2back_gemm", &back2back_gemm_op);
     m.impl("lstm_cell", &lstm_cell_op);

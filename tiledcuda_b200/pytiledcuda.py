@@ -11,6 +11,7 @@ src/kernels/scatter_nd.cu:107).
 """
 from __future__ import annotations
 
+import math
 import os
 from pathlib import Path
 
@@ -34,6 +35,19 @@ def flash_attn(Q, K, V, O, scale=None, v_is_transposed=False):
     if scale is None:
         scale = Q.shape[-1] ** -0.5
     torch.ops.tiledcuda.flash_attn(Q, K, V, O, float(scale), bool(v_is_transposed))
+
+
+def flash_attn_ex(Q, K, V, O, scale=None, causal=False, seq_major=False):
+    """flash_attn with a bottom-right aligned causal mask and / or [B, S, H, D] operands."""
+    if scale is None:
+        scale = 1.0 / math.sqrt(Q.shape[-1])
+    torch.ops.tiledcuda.flash_attn_ex(Q, K, V, O, float(scale), bool(causal), bool(seq_major))
+
+
+def scatter_nd_add(scatter_data, scatter_indices, scatter_updates):
+    """Accumulating scatter, what the reference's kernel does (src/kernels/scatter_nd.cu:44-47); argument order as
+    scatter_nd."""
+    torch.ops.tiledcuda.scatter_nd_add(scatter_data, scatter_updates, scatter_indices)
 
 
 def gemm(A, B, C):
