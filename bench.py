@@ -204,6 +204,11 @@ class Workload:
         raise NotImplementedError
 
 
+def rotation_sets(footprint_bytes: int) -> int:
+    """How many copies of a workload's buffers make one pass over them exceed L2 (126 MB) with margin."""
+    return 1 if footprint_bytes > 126e6 else int(-(-160e6 // footprint_bytes))
+
+
 class GemmWorkload(Workload):
     def __init__(self, n: int):
         self.n = n
@@ -213,6 +218,9 @@ class GemmWorkload(Workload):
     def units_per_step(self):
         return 2.0 * self.n ** 3
 
+    def footprint(self):
+        return 2 * self.n * self.n * 2 + self.n * self.n * 4
+
     def setup(self, device, rank):
         n = self.n
         g = torch.Generator(device=device).manual_seed(SEED + rank)
@@ -220,17 +228,28 @@ class GemmWorkload(Workload):
         gb = torch.Generator(device=device).manual_seed(SEED)
         self.b = (torch.rand(n, n, generator=gb, device=device) * 2 - 1).half()
         self.c = torch.empty(n, n, device=device)
+        # small problems: enough copies of the operands and outputs that one pass over them exceeds L2, used in
+        # rotation, so that every step reads cold data while the code stays warm
+        self.sets = [(self.a, self.b, self.c)]
+        for _ in range(rotation_sets(self.footprint()) - 1):
+            self.sets.append((self.a.clone(), self.b.clone(), torch.empty_like(self.c)))
+        self.turn = 0
 
     def step(self):
         from tiledcuda_b200 import ops
-        ops.gemm(self.a, self.b, self.c)
+        a, b, c = self.sets[self.turn]
+        self.turn = (self.turn + 1) % len(self.sets)
+        ops.gemm(a, b, c)
 
     def describe(self):
         n = self.n
-        footprint = 2 * n * n * 2 + n * n * 4
+        sets = rotation_sets(self.footprint())
         return {"M_per_gpu": n, "N": n, "K": n, "a": "row-major fp16", "b": "col-major fp16 ([N,K] rows)", "c": "fp32",
-                "l2": "inputs+output larger than L2" if footprint > 126e6 else "L2 flushed between steps",
-                "flush_l2": footprint <= 126e6}
+                "l2": "inputs+output larger than L2" if sets == 1 else
+                      f"{sets} operand/output sets of {self.footprint() / 1e6:.1f} MB used in rotation (together larger than L2)",
+                "flush_l2": False,
+                # a step of a few microseconds: a CUDA graph of one pass over the sets replaces the Python call path
+                **({"graph_steps": sets, "launch": f"CUDA graph of {sets} steps"} if n <= 2048 else {})}
 
     def e2e_setup(self):
         from tiledcuda_b200 import ops
@@ -277,10 +296,22 @@ class B2bWorkload(Workload):
         self.b = (torch.randn(128, 128, generator=g, device=device) * 0.1).half()
         self.d = (torch.randn(128, 128, generator=g, device=device) * 0.1).half()
         self.e = torch.empty(16384, 128, device=device)
+        self.sets = [(self.a, self.b, self.d, self.e)]
+        for _ in range(rotation_sets(self.bytes_per_step()) - 1):
+            self.sets.append((self.a.clone(), self.b.clone(), self.d.clone(), torch.empty_like(self.e)))
+        self.turn = 0
 
     def step(self):
         from tiledcuda_b200 import ops
-        ops.back2back_gemm(self.a, self.b, self.d, self.e)
+        a, b, d, e = self.sets[self.turn]
+        self.turn = (self.turn + 1) % len(self.sets)
+        ops.back2back_gemm(a, b, d, e)
+
+    def describe(self):
+        sets = rotation_sets(self.bytes_per_step())
+        return {"M": 16384, "N": 128, "K": 128, "P": 128,
+                "l2": f"{sets} operand/output sets of {self.bytes_per_step() / 1e6:.1f} MB used in rotation (together larger than L2)",
+                "flush_l2": False, "graph_steps": sets, "launch": f"CUDA graph of {sets} steps"}
 
     def cpu_sample(self):
         a, b, d = self.a.cpu().float(), self.b.cpu().float(), self.d.cpu().float()
@@ -418,12 +449,36 @@ def flush_l2(device, scratch=[None]):
     scratch[0].fill_(1)
 
 
-def time_steps(fn, steps: int, warmup: int, barrier, flush=False, device=None, on_timed_start=None) -> float:
-    """Milliseconds per step on the device, CUDA events on the launching stream, barrier + sync on both sides."""
+def time_steps(fn, steps: int, warmup: int, barrier, flush=False, device=None, on_timed_start=None, graph: int = 0) -> float:
+    """Milliseconds per step on the device, CUDA events on the launching stream, barrier + sync on both sides.
+    graph = G > 0: G consecutive steps are captured into one CUDA graph and the timed region replays it
+    ceil(steps / G) times (for kernels of a few microseconds, which the Python call path cannot feed fast enough)."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     barrier()
+    if graph > 0:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(graph):
+                    fn()
+        torch.cuda.current_stream().wait_stream(side)
+        g.replay()
+        torch.cuda.synchronize()
+        replays = -(-steps // graph)
+        if on_timed_start is not None:
+            on_timed_start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(replays):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        barrier()
+        return e0.elapsed_time(e1) / (replays * graph)
     if on_timed_start is not None:
         on_timed_start()
     if flush:
@@ -617,7 +672,7 @@ def main() -> int:
 
     sampler = ClockSampler(local_rank)
     ms = time_steps(w.step, args.steps, args.warmup, barrier, flush=bool(desc.get("flush_l2")), device=device,
-                    on_timed_start=sampler.start)
+                    on_timed_start=sampler.start, graph=int(desc.get("graph_steps", 0)))
     clocks = sampler.stop()
     burst_ms = best_of_steps(w.step, 10, barrier) if (w.bound == "tensor" and w.launches_per_step() == 1) else None
     status = _lib.device_status()
@@ -666,7 +721,8 @@ def main() -> int:
         "config": {"workload": w.name, **desc, "parallelism": f"dp{world} (row slabs, no data-path collective)"},
         "roofline": roofline(w, ms, peaks, burst_ms),
         "clocks": clocks,
-        "gpu_launches": args.steps * w.launches_per_step(),
+        "gpu_launches": (-(-args.steps // int(desc["graph_steps"])) * int(desc["graph_steps"]) if desc.get("graph_steps")
+                         else args.steps) * w.launches_per_step(),
         "device_status": status,
     }
     if e2e is not None:
@@ -687,8 +743,10 @@ def main() -> int:
                 ow = make_workload(name)
                 ow.setup(device, 0)
                 od = ow.describe()
-                steps = 10 if name != "gemm16384" else 5
-                oms = time_steps(ow.step, steps, 3, barrier, flush=bool(od.get("flush_l2")), device=device)
+                # short kernels need many launches for the host to stay ahead of the device
+                steps = {"gemm16384": 5, "gemm1024": 300, "gemm2048": 200, "b2b": 300}.get(name, 10)
+                ograph = int(od.get("graph_steps", 0))
+                oms = time_steps(ow.step, steps, 3, barrier, flush=bool(od.get("flush_l2")), device=device, graph=ograph)
                 oscale = 1e12 if ow.unit == "TFLOP/s" else 1e9
                 others[name] = {"metric": ow.metric, "value": round(ow.units_per_step() / (oms * 1e-3) / oscale, 2), "unit": ow.unit,
                                 "ms_per_step": round(oms, 4), "roofline": roofline(ow, oms, peaks), "launches_per_step": ow.launches_per_step()}
