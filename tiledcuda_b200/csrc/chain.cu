@@ -21,6 +21,8 @@
 // Q is loaded once, and O is divided by the running sum once instead of once per KV block.
 #include <math.h>
 
+#include <string.h>
+
 #include "host.h"
 #include "sm100.cuh"
 
@@ -44,12 +46,13 @@ struct ChainParams {
     void* out;       // fp16 [batch, rows, dv] (attention) or fp32 (B2B)
     float* lse;      // optional, attention only
     uint32_t* status;
+    int store_by_tma;  // B2B: fp32 output through shared memory and TMA stores (tmap_o is valid)
 };
 
 template <bool kSoftmax, bool kVTrans>
 __global__ void __launch_bounds__(kChThreads, 1)
 chain_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-             const __grid_constant__ CUtensorMap tmap_v, const ChainParams p) {
+             const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o, const ChainParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align_smem_1024(smem_raw);
     uint8_t* s_q = smem;
@@ -304,26 +307,55 @@ chain_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__
             tc_fence_after_sync();
             const float inv_l = kSoftmax ? (1.f / l_sum) : 1.f;
             const int64_t out_row = static_cast<int64_t>(bh) * p.rows + row;
+            if (!kSoftmax && p.store_by_tma) {
+                // fp32 result: 32 x 32 boxes through shared memory (128-byte swizzle) and TMA stores of whole
+                // lines. Every MMA has completed, so the operand tile of the second product is free to stage in;
+                // TMA clips boxes at the edges of the output.
+                uint8_t* stage = s_p + quarter * 8192;
+                int sbuf = 0;
+                if (lane == 0) tma_prefetch_desc(&tmap_o);
 #pragma unroll 1
-            for (int c = 0; c < p.dv / 16; ++c) {
-                uint32_t r[16];
-                tmem_ld_x16(tmem_o + lane_base + static_cast<uint32_t>(c * 16), r);
-                tmem_ld_wait();
-                if (row < p.rows) {
-                    if (kSoftmax) {
-                        uint32_t h[8];
+                for (int c = 0; c < (p.dv + 31) / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_x32(tmem_o + lane_base + static_cast<uint32_t>(c * 32), r);
+                    tmem_ld_wait();
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
+                    uint8_t* box = stage + sbuf * 4096 + lane * 128;
 #pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            h[i] = pack_half2(__uint_as_float(r[2 * i]) * inv_l, __uint_as_float(r[2 * i + 1]) * inv_l);
-                        uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(p.out) + out_row * p.dv + c * 16);
-                        dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
-                        dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
-                    } else {
-                        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + out_row * p.dv + c * 16);
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<uint4*>(box + ((j ^ (lane & 7)) << 4)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (q0 + quarter * 32 < p.rows) tma_store_3d(&tmap_o, stage + sbuf * 4096, c * 32, q0 + quarter * 32, bh);
+                        tma_store_commit();
+                    }
+                    sbuf ^= 1;
+                }
+                if (lane == 0) tma_store_wait<0>();
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < p.dv / 16; ++c) {
+                    uint32_t r[16];
+                    tmem_ld_x16(tmem_o + lane_base + static_cast<uint32_t>(c * 16), r);
+                    tmem_ld_wait();
+                    if (row < p.rows) {
+                        if (kSoftmax) {
+                            uint32_t h[8];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                                                 __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                            for (int i = 0; i < 8; ++i)
+                                h[i] = pack_half2(__uint_as_float(r[2 * i]) * inv_l, __uint_as_float(r[2 * i + 1]) * inv_l);
+                            uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(p.out) + out_row * p.dv + c * 16);
+                            dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
+                            dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
+                        } else {
+                            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + out_row * p.dv + c * 16);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                                     __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                        }
                     }
                 }
             }
@@ -378,8 +410,17 @@ static int launch_chain(const void* Q, const void* K, const void* V, void* out, 
     p.out = out;
     p.lse = lse;
     p.status = dev->status_word;
+    CUtensorMap to;
+    memset(&to, 0, sizeof(to));
+    p.store_by_tma = 0;
+    if (!kSoftmax && aligned16(out) && dv % 4 == 0) {
+        if (int rc = encode_tmap_f32_sw128_3d(&to, out, static_cast<uint64_t>(dv), static_cast<uint64_t>(rows),
+                                              static_cast<uint64_t>(batch), 32, 32))
+            return rc;
+        p.store_by_tma = 1;
+    }
     const dim3 grid(static_cast<unsigned>((rows + kChBM - 1) / kChBM), static_cast<unsigned>(batch));
-    kernel<<<grid, kChThreads, kChSmem, stream>>>(tq, tk, tv, p);
+    kernel<<<grid, kChThreads, kChSmem, stream>>>(tq, tk, tv, to, p);
     TCB_CUDA(cudaGetLastError());
     return TC_OK;
 }

@@ -107,6 +107,22 @@ int encode_tmap_f32_sw128(CUtensorMap* out, const void* base, uint64_t cols, uin
     return TC_OK;
 }
 
+int encode_tmap_f32_sw128_3d(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint64_t batch,
+                             uint32_t box_cols, uint32_t box_rows) {
+    if (int rc = load_encode()) return rc;
+    const cuuint64_t gdim[3] = {cols, rows, batch};
+    const cuuint64_t gstride[2] = {cols * 4, rows * cols * 4};
+    const cuuint32_t bdim[3] = {box_cols, box_rows, 1};
+    const cuuint32_t estride[3] = {1, 1, 1};
+    CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), gdim, gstride, bdim, estride,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(TC_ERR_CUDA, "cuTensorMapEncodeTiled (fp32 output, 3-D) failed with CUresult %d (%llu x %llu x %llu)",
+                    static_cast<int>(r), (unsigned long long)cols, (unsigned long long)rows, (unsigned long long)batch);
+    return TC_OK;
+}
+
 }  // namespace tcb
 
 extern "C" {

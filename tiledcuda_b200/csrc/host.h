@@ -49,6 +49,10 @@ int encode_tmap_f16_sw128(CUtensorMap* out, const void* base, int rank, const ui
 int encode_tmap_f32_sw128(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint64_t row_stride_bytes,
                           uint32_t box_cols, uint32_t box_rows);
 
+// The same for a [batch, rows, cols] fp32 array (cols innermost, dense): boxes of box_cols x box_rows x 1.
+int encode_tmap_f32_sw128_3d(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint64_t batch,
+                             uint32_t box_cols, uint32_t box_rows);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace tcb
