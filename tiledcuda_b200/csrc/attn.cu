@@ -220,15 +220,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 if (n_halves > 1) issue_s(1);
                 if (leader) umma_commit(&bar_kv_empty[kv_stage(0)]);
             }
+            // The K / V barriers that an even half block needs are awaited at the end of the iteration before it:
+            // they have long completed by then, but even a completed wait costs the issuing thread a couple of
+            // hundred cycles, and there it overlaps the softmax instead of delaying the MMAs behind P.
+            auto await_kv = [&](int g) -> bool {
+                if ((g & 1) != 0 || g >= n_halves) return true;
+                const int j = g >> 1;
+                if (!mbar_wait(&bar_kv_full[kv_stage(2 * j + 1)], kv_phase(2 * j + 1), abort_word, kDevTimeoutMma)) return false;
+                return g + 2 >= n_halves ||
+                       mbar_wait(&bar_kv_full[kv_stage(2 * j + 2)], kv_phase(2 * j + 2), abort_word, kDevTimeoutMma);
+            };
+            ok = ok && await_kv(0);
             for (int g = 0; ok && g < n_halves; ++g) {
                 const int j = g >> 1;
                 const bool more_s = g + 2 < n_halves;
-                if ((g & 1) == 0) {
-                    if (!mbar_wait(&bar_kv_full[kv_stage(2 * j + 1)], kv_phase(2 * j + 1), abort_word, kDevTimeoutMma)) break;
-                    if (more_s &&
-                        !mbar_wait(&bar_kv_full[kv_stage(2 * j + 2)], kv_phase(2 * j + 2), abort_word, kDevTimeoutMma))
-                        break;
-                }
                 if (!mbar_wait(&bar_p_full[t * 2 + (g & 1)], static_cast<uint32_t>((g >> 1) & 1), abort_word, kDevTimeoutMma)) break;
                 tc_fence_after_sync();
                 issue_pv(g);
@@ -241,6 +246,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     if (more_s && (((g + 2) & 1) == 1 || g + 2 == n_halves - 1))
                         umma_commit(&bar_kv_empty[kv_stage(2 * ((g + 2) >> 1))]);
                 }
+                if (!await_kv(g + 1)) break;
             }
         }
         __syncwarp();

@@ -32,6 +32,11 @@ struct GemmSmem {
     static constexpr int kABytes = kGemmBM * kGemmBK * 2;
     static constexpr int kBBytes = BN * kGemmBK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
+    // STAGES counts K blocks of capacity. With BN = 128 a K block is four 64-cycle MMAs, less than the ~200 cycles
+    // a barrier wait costs the producer or the issuing thread even on a completed phase, so two K blocks share
+    // one ring stage and one barrier; with BN = 256 a K block is 512 cycles of MMA and the wait hides behind it.
+    static constexpr int kSub = (BN <= 128 && STAGES % 2 == 0) ? 2 : 1;
+    static constexpr int kRing = STAGES / kSub;
     static constexpr int kBarBytes = 256;
     static constexpr int kTotal = STAGES * kStageBytes + kStoreStageBytes + kBarBytes + 1024;  // + slack for 1024-B alignment
 };
@@ -101,15 +106,19 @@ gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
                 int tm, tn;
                 gemm_tile_coords(tile, tiles_m, tiles_n, tm, tn);
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = 0; kb < k_blocks; kb += S::kSub) {
                     if (!mbar_wait(&bar_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) {
                         ok = false;
                         break;
                     }
-                    mbar_arrive_expect_tx(&bar_full[stage], S::kStageBytes);
-                    tma_load_2d(smem_a + stage * S::kABytes, &tmap_a, &bar_full[stage], kb * kGemmBK, tm * kGemmBM);
-                    tma_load_2d(smem_b + stage * S::kBBytes, &tmap_b, &bar_full[stage], kb * kGemmBK, tn * BN);
-                    if (++stage == STAGES) {
+                    const int subs = min(S::kSub, k_blocks - kb);
+                    mbar_arrive_expect_tx(&bar_full[stage], static_cast<uint32_t>(subs * S::kStageBytes));
+                    for (int sub = 0; sub < subs; ++sub) {
+                        const int slot = stage * S::kSub + sub;
+                        tma_load_2d(smem_a + slot * S::kABytes, &tmap_a, &bar_full[stage], (kb + sub) * kGemmBK, tm * kGemmBM);
+                        tma_load_2d(smem_b + slot * S::kBBytes, &tmap_b, &bar_full[stage], (kb + sub) * kGemmBK, tn * BN);
+                    }
+                    if (++stage == S::kRing) {
                         stage = 0;
                         phase ^= 1u;
                     }
@@ -121,6 +130,8 @@ gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             const uint32_t idesc = make_idesc_f16_f32(kGemmBM, BN, false, false) | idesc_extra;
+            const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem_a), 16, 1024);
+            const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem_b), 16, 1024);
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -130,22 +141,27 @@ gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 if (!mbar_wait(&bar_acc_empty[acc], acc_phase ^ 1u, abort_word, kDevTimeoutMma)) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = 0; kb < k_blocks; kb += S::kSub) {
                     if (!mbar_wait(&bar_full[stage], phase, abort_word, kDevTimeoutMma)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + stage * S::kABytes), 16, 1024);
-                    const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem_b + stage * S::kBBytes), 16, 1024);
+                    const int subs = min(S::kSub, k_blocks - kb);
+                    for (int sub = 0; sub < subs; ++sub) {
+                        // the descriptor of a slot is that of slot 0 plus a constant (address field in 16-byte units)
+                        const int slot = stage * S::kSub + sub;
+                        const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(slot * (S::kABytes >> 4));
+                        const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(slot * (S::kBBytes >> 4));
 #pragma unroll
-                    for (int k = 0; k < kGemmBK / 16; ++k) {
-                        // +32 bytes per K=16 step inside the 128-byte swizzle row (address field is in 16-B units)
-                        umma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2),
-                                    idesc, (kb | k) != 0);
+                        for (int k = 0; k < kGemmBK / 16; ++k) {
+                            // +32 bytes per K=16 step inside the 128-byte swizzle row
+                            umma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2),
+                                        idesc, (kb | sub | k) != 0);
+                        }
                     }
                     umma_commit(&bar_empty[stage]);
-                    if (++stage == STAGES) {
+                    if (++stage == S::kRing) {
                         stage = 0;
                         phase ^= 1u;
                     }

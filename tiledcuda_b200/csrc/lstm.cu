@@ -32,7 +32,12 @@ struct LstmCfg {
     static constexpr int kABytes = kLstmBM * kLstmBK * 2;
     static constexpr int kGateBytes = HT * kLstmBK * 2;
     static constexpr int kBBytes = 4 * kGateBytes;
-    static constexpr int kStageBytes = kABytes + kBBytes;
+    // A stage of the ring holds kSub K blocks (each a 64-wide swizzled box per operand) behind ONE barrier: a
+    // barrier wait costs either side about 200 cycles even when the phase has completed, against 48 (N = 64) or
+    // 64 (N = 128) cycles per MMA, and the tensor pipe runs dry while the issuing thread waits.
+    static constexpr int kSub = kN <= 128 ? 2 : 1;
+    static constexpr int kBlockBytes = kABytes + kBBytes;
+    static constexpr int kStageBytes = kSub * kBlockBytes;
     static constexpr int kStages = (192 * 1024) / kStageBytes;
     static constexpr int kSmem = kStages * kStageBytes + 256 + 1024;
     static constexpr int kTmemCols = kN < 32 ? 32 : kN;
@@ -62,7 +67,7 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align_smem_1024(smem_raw);
     uint8_t* smem_a = smem;
-    uint8_t* smem_b = smem + Cfg::kStages * Cfg::kABytes;
+    uint8_t* smem_b = smem + Cfg::kStages * Cfg::kSub * Cfg::kABytes;
     uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
     uint64_t* bar_empty = bar_full + Cfg::kStages;
     uint64_t* bar_acc_full = bar_empty + Cfg::kStages;
@@ -104,22 +109,31 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             tma_prefetch_desc(&tmap_u);
             int stage = 0;
             uint32_t phase = 0;
+            auto load_b = [&](int kbs, int slot, uint64_t* bar) {
+                // one 3-D box {64 k, HT units, 4 gates}: the four gate slabs land side by side, gate-major
+                const bool from_x = kbs < kb_x;
+                const int part = from_x ? kb_x : kb_h;
+                const int kcoord = ((from_x ? kbs : kbs - kb_x) + static_cast<int>(blockIdx.x)) % part * kLstmBK;
+                tma_load_3d(smem_b + slot * Cfg::kBBytes, from_x ? &tmap_w : &tmap_u, bar, kcoord, j0, 0);
+            };
             // h_prev (and c_prev, read by the epilogue) come from the previous launch in the stream: with
             // programmatic dependent launch everything above overlapped its tail, the data is awaited here.
             grid_dependency_wait();
-            for (int kb = 0; kb < k_blocks; ++kb) {
+            for (int kb = 0; kb < k_blocks; kb += Cfg::kSub) {
                 if (!mbar_wait(&bar_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) break;
-                // Every CTA of a batch tile reads the same x / h tiles: each starts at a different K block
-                // and wraps around, so that at any moment the CTAs pull different lines out of L2.
-                const bool from_x = kb < kb_x;
-                const CUtensorMap* ta = from_x ? &tmap_x : &tmap_h;
-                const CUtensorMap* tb = from_x ? &tmap_w : &tmap_u;
-                const int part = from_x ? kb_x : kb_h;
-                const int kcoord = ((from_x ? kb : kb - kb_x) + static_cast<int>(blockIdx.x)) % part * kLstmBK;
-                mbar_arrive_expect_tx(&bar_full[stage], Cfg::kStageBytes);
-                tma_load_2d(smem_a + stage * Cfg::kABytes, ta, &bar_full[stage], kcoord, b0);
-                // one 3-D box {64 k, HT units, 4 gates}: the four gate slabs land side by side, gate-major
-                tma_load_3d(smem_b + stage * Cfg::kBBytes, tb, &bar_full[stage], kcoord, j0, 0);
+                const int subs = min(Cfg::kSub, k_blocks - kb);
+                mbar_arrive_expect_tx(&bar_full[stage], static_cast<uint32_t>(subs * Cfg::kBlockBytes));
+                for (int sub = 0; sub < subs; ++sub) {
+                    // Every CTA of a batch tile reads the same x / h tiles: each starts at a different K block
+                    // and wraps around, so that at any moment the CTAs pull different lines out of L2.
+                    const int kbs = kb + sub;
+                    const bool from_x = kbs < kb_x;
+                    const int part = from_x ? kb_x : kb_h;
+                    const int kcoord = ((from_x ? kbs : kbs - kb_x) + static_cast<int>(blockIdx.x)) % part * kLstmBK;
+                    const int slot = stage * Cfg::kSub + sub;
+                    tma_load_2d(smem_a + slot * Cfg::kABytes, from_x ? &tmap_x : &tmap_h, &bar_full[stage], kcoord, b0);
+                    load_b(kbs, slot, &bar_full[stage]);
+                }
                 if (++stage == Cfg::kStages) {
                     stage = 0;
                     phase ^= 1u;
@@ -130,21 +144,29 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc_f16_f32(kLstmBM, Cfg::kN, false, false);
+            // The descriptors of a slot are those of slot 0 plus a constant: no address arithmetic between MMAs,
+            // which the pipe would wait for (the issuing thread runs barely one MMA ahead of it).
+            const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem_a), 16, 1024);
+            const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem_b), 16, 1024);
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int kb = 0; kb < k_blocks; ++kb) {
+            for (int kb = 0; kb < k_blocks; kb += Cfg::kSub) {
                 if (!mbar_wait(&bar_full[stage], phase, abort_word, kDevTimeoutMma)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after_sync();
-                const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + stage * Cfg::kABytes), 16, 1024);
-                const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem_b + stage * Cfg::kBBytes), 16, 1024);
+                const int subs = min(Cfg::kSub, k_blocks - kb);
+                for (int sub = 0; sub < subs; ++sub) {
+                    const int slot = stage * Cfg::kSub + sub;
+                    const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(slot * (Cfg::kABytes >> 4));
+                    const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(slot * (Cfg::kBBytes >> 4));
 #pragma unroll
-                for (int k = 0; k < kLstmBK / 16; ++k)
-                    umma_f16_ss(tmem_base, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2),
-                                idesc, (kb | k) != 0);
+                    for (int k = 0; k < kLstmBK / 16; ++k)
+                        umma_f16_ss(tmem_base, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2),
+                                    idesc, (kb | sub | k) != 0);
+                }
                 umma_commit(&bar_empty[stage]);
                 if (++stage == Cfg::kStages) {
                     stage = 0;
