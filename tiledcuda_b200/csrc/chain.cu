@@ -110,6 +110,9 @@ chain_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_s0 = tmem_base;          // S buffers: columns [0,128) and [128,256)
     const uint32_t tmem_o = tmem_base + 256;     // O accumulator: columns [256, 256 + dv)
+    // No global memory has been touched yet: a kernel queued behind this one may start its set-up on free SMs,
+    // and this one waits for its predecessor only before its first load (producer) or store (row threads).
+    grid_launch_dependents();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -117,6 +120,7 @@ chain_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__
             tma_prefetch_desc(&tmap_q);
             tma_prefetch_desc(&tmap_k);
             tma_prefetch_desc(&tmap_v);
+            grid_dependency_wait();
             mbar_arrive_expect_tx(bar_q_full, static_cast<uint32_t>(k_chunks * kChChunk));
             for (int c = 0; c < k_chunks; ++c) tma_load_3d(s_q + c * kChChunk, &tmap_q, bar_q_full, c * 64, q0, bh);
             const uint32_t v_bytes = kVTrans ? static_cast<uint32_t>(2 * p.dv * 128) : static_cast<uint32_t>(v_chunks * kChChunk);
@@ -207,6 +211,7 @@ chain_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__
         float m_used = -INFINITY;  // running maximum the exponentials are taken against (log2 units)
         float l_sum = 0.f;         // running sum of exponentials
         bool ok = true;
+        grid_dependency_wait();
 
         for (int j = 0; j < n_blocks; ++j) {
             const int buf = j & 1;
@@ -420,8 +425,7 @@ static int launch_chain(const void* Q, const void* K, const void* V, void* out, 
         p.store_by_tma = 1;
     }
     const dim3 grid(static_cast<unsigned>((rows + kChBM - 1) / kChBM), static_cast<unsigned>(batch));
-    kernel<<<grid, kChThreads, kChSmem, stream>>>(tq, tk, tv, to, p);
-    TCB_CUDA(cudaGetLastError());
+    TCB_CUDA(launch_overlapped(kernel, grid, dim3(kChThreads), kChSmem, stream, tq, tk, tv, to, p));
     return TC_OK;
 }
 

@@ -94,12 +94,17 @@ gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above touched no global memory. A kernel queued behind this one may now start its own set-up
+    // on SMs this grid leaves free; this kernel in turn waits for the one before it only where it first reads
+    // (the producer) or writes (the epilogue) global memory.
+    grid_launch_dependents();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             tma_prefetch_desc(&tmap_a);
             tma_prefetch_desc(&tmap_b);
+            grid_dependency_wait();
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -184,6 +189,7 @@ gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         uint8_t* stage = smem_store + quarter * 8192;
         const bool use_tma = use_tma_store != 0;
         if (use_tma && lane == 0) tma_prefetch_desc(&tmap_c);
+        grid_dependency_wait();
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
             int tm, tn;
             gemm_tile_coords(tile, tiles_m, tiles_n, tm, tn);
@@ -229,9 +235,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, float* C, i
     CUtensorMap tc;
     int use_tma = 0;
     if (int rc = output_store_map(&tc, &use_tma, C, M, N, ldc)) return rc;
-    kernel<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, tc, C, M, N, K, ldc, tiles_m, tiles_n, dev->status_word, idesc_extra,
-                                                      use_tma);
-    TCB_CUDA(cudaGetLastError());
+    TCB_CUDA(launch_overlapped(kernel, dim3(grid), dim3(kGemmThreads), S::kTotal, stream, ta, tb, tc, C, M, N, K, ldc, tiles_m,
+                               tiles_n, dev->status_word, idesc_extra, use_tma));
     return TC_OK;
 }
 

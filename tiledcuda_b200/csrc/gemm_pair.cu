@@ -89,12 +89,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     cluster_sync_all();   // barriers of both CTAs are initialised before anyone signals across the pair
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // No global memory touched so far: a kernel queued behind this one may begin its set-up; this one waits for
+    // its predecessor where the producer first loads and where the epilogue first stores.
+    grid_launch_dependents();
 
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
         if (lane == 0) {
             tma_prefetch_desc(&tmap_a);
             tma_prefetch_desc(&tmap_b);
+            grid_dependency_wait();
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -182,6 +186,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         uint8_t* stage = smem_store + quarter * 8192;
         const bool use_tma = use_tma_store != 0;
         if (use_tma && lane == 0) tma_prefetch_desc(&tmap_c);
+        grid_dependency_wait();
         for (int tile = pair; tile < num_tiles; tile += num_pairs) {
             int tm, tn;
             pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
@@ -270,12 +275,16 @@ gemm_pair_tall_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     cluster_sync_all();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // No global memory touched so far: a kernel queued behind this one may begin its set-up; this one waits for
+    // its predecessor where the producer first loads and where the epilogue first stores.
+    grid_launch_dependents();
 
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
         if (lane == 0) {
             tma_prefetch_desc(&tmap_a);
             tma_prefetch_desc(&tmap_b);
+            grid_dependency_wait();
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -364,6 +373,7 @@ gemm_pair_tall_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         uint8_t* stage = smem_store + quarter * 8192;
         const bool use_tma = use_tma_store != 0;
         if (use_tma && lane == 0) tma_prefetch_desc(&tmap_c);
+        grid_dependency_wait();
         for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
             int tm, tn;
             pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
@@ -411,9 +421,8 @@ int launch_gemm_pair_tall(const CUtensorMap& ta, const CUtensorMap& tb, float* C
     const int tiles = tiles_m * tiles_n;
     const int max_pairs = dev->sm_count / 2;
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
-    gemm_pair_tall_kernel<<<2 * pairs, kPairThreads, kTallSmem, stream>>>(ta, tb, tc, C, M, N, K, ldc, tiles_m, tiles_n,
-                                                                         dev->status_word, idesc_extra, use_tma);
-    TCB_CUDA(cudaGetLastError());
+    TCB_CUDA(launch_overlapped(gemm_pair_tall_kernel, dim3(2 * pairs), dim3(kPairThreads), kTallSmem, stream, ta, tb, tc, C, M, N,
+                               K, ldc, tiles_m, tiles_n, dev->status_word, idesc_extra, use_tma));
     return TC_OK;
 }
 
@@ -432,9 +441,8 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int
     const int tiles = tiles_m * tiles_n;
     const int max_pairs = dev->sm_count / 2;
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
-    gemm_pair_kernel<<<2 * pairs, kPairThreads, kPairSmem, stream>>>(ta, tb, tc, C, M, N, K, ldc, tiles_m, tiles_n,
-                                                                    dev->status_word, idesc_extra, use_tma);
-    TCB_CUDA(cudaGetLastError());
+    TCB_CUDA(launch_overlapped(gemm_pair_kernel, dim3(2 * pairs), dim3(kPairThreads), kPairSmem, stream, ta, tb, tc, C, M, N, K,
+                               ldc, tiles_m, tiles_n, dev->status_word, idesc_extra, use_tma));
     return TC_OK;
 }
 

@@ -55,4 +55,24 @@ int encode_tmap_f32_sw128_3d(CUtensorMap* out, const void* base, uint64_t cols, 
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Launch with programmatic stream serialization: if the kernel before it in the stream releases its dependents
+// early (griddepcontrol.launch_dependents), this kernel's CTAs may start on free SMs and run their set-up while
+// that kernel drains. The kernel must execute griddepcontrol.wait before it touches global memory; behind a kernel
+// that never releases early the launch behaves like a plain one.
+template <typename... Params, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
 }  // namespace tcb
