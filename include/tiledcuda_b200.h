@@ -58,10 +58,11 @@ int tc_gemm_bf16_f32(const void* A, const void* B, void* C, int64_t M, int64_t N
  * (examples/python/gemm/main.py:37-70 with compile.py:83-127); here the table is fixed ahead of time from
  * measurements. */
 enum {
-    TC_GEMM_TILE_128x128 = 0,       /* lone CTA, 128x128x64, six stages */
+    TC_GEMM_TILE_128x128 = 0,       /* lone CTA, 128x128, six K blocks of 64 in flight */
     TC_GEMM_TILE_128x256 = 1,       /* lone CTA, 128x256x64, four stages */
     TC_GEMM_TILE_PAIR_256x256 = 2,  /* CTA pair, tcgen05.mma.cta_group::2, double-buffered accumulators */
-    TC_GEMM_TILE_PAIR_512x256 = 3   /* CTA pair, two accumulator halves per CTA */
+    TC_GEMM_TILE_PAIR_512x256 = 3,  /* CTA pair, two accumulator halves per CTA */
+    TC_GEMM_TILE_128x64 = 4         /* lone CTA, 128x64: problems whose 128x128 tiles would leave half the SMs idle */
 };
 int tc_gemm_tile_plan(int64_t M, int64_t N, int64_t K, int sm_count);
 

@@ -90,14 +90,16 @@ def test_check_raises_with_the_library_message():
 
 def test_gemm_tile_plan_is_a_pure_function_and_parity_shapes_cover_every_tile():
     """tc_gemm_tile_plan needs no GPU. The headline size takes the tall pair tiles, mid sizes the square pair
-    tiles, small ones lone CTAs; and the GEMM shapes of the GPU parity suite reach all four kernels."""
+    tiles, small ones lone CTAs (128x64 tiles while 128x128 ones would leave half the SMs idle); and the GEMM
+    shapes of the GPU parity suite reach all five kernels."""
     lib = _lib.load()
     plan = lambda m, n, k: lib.tc_gemm_tile_plan(m, n, k, 148)
     assert plan(8192, 8192, 8192) == 3 and plan(16384, 16384, 16384) == 3
     assert plan(4096, 4096, 4096) == 2 and plan(2048, 2048, 2048) == 2 and plan(8192, 8192, 2048) == 2
-    assert plan(1024, 1024, 1024) == 0 and plan(16, 16, 16) == 0 and plan(100000, 64, 512) == 0
+    assert plan(1024, 1024, 1024) == 4 and plan(16, 16, 16) == 4 and plan(100000, 64, 512) == 4
+    assert plan(1536, 1536, 1536) == 0 and plan(2304, 2304, 64) == 0
     assert plan(128, 19200, 256) == 1
     assert lib.tc_gemm_tile_plan(0, 8, 8, 148) == -1 and lib.tc_gemm_tile_plan(8, 8, 8, 0) == -1
     from tests.test_gpu_parity import GEMM_SHAPES
     kinds = {plan(*shape) for shape in GEMM_SHAPES} | {plan(16384 + 328, 16384 - 56, 8192)}  # + the tall-tile test
-    assert kinds == {0, 1, 2, 3}
+    assert kinds == {0, 1, 2, 3, 4}

@@ -269,7 +269,12 @@ int gemm_tile_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
         const int64_t tiles_tall = ((M + 511) / 512) * ((N + 255) / 256);
         return (K >= 4096 && tiles_tall >= 4 * pairs) ? TC_GEMM_TILE_PAIR_512x256 : TC_GEMM_TILE_PAIR_256x256;
     }
-    return (N <= 128 || cost_128 <= cost_256) ? TC_GEMM_TILE_128x128 : TC_GEMM_TILE_128x256;
+    if (N > 128 && cost_128 > cost_256) return TC_GEMM_TILE_128x256;
+    // A single partial wave of 128x128 tiles: halving the tile width doubles the busy SMs, and although an N = 64
+    // MMA runs at two thirds of the rate (shared-memory bound) each CTA's K loop and epilogue get shorter.
+    const int64_t tiles64 = ((M + 127) / 128) * ((N + 63) / 64);
+    if (N <= 64 || (2 * tiles128 <= sm_count && tiles64 <= sm_count)) return TC_GEMM_TILE_128x64;
+    return TC_GEMM_TILE_128x128;
 }
 
 // The dispatch of tc_gemm_f16_f32 for a caller that brings its own device record (and therefore its own
@@ -284,7 +289,7 @@ int gemm_f16_f32_on(const DeviceInfo* dev, const void* A, const void* B, float* 
         if (plan == TC_GEMM_TILE_PAIR_512x256 && force[0] == 's') plan = TC_GEMM_TILE_PAIR_256x256;
     }
     const bool use_pair = plan == TC_GEMM_TILE_PAIR_256x256 || plan == TC_GEMM_TILE_PAIR_512x256;
-    const uint32_t bn = plan == TC_GEMM_TILE_128x256 ? 256u : 128u;
+    const uint32_t bn = plan == TC_GEMM_TILE_128x256 ? 256u : (plan == TC_GEMM_TILE_128x64 ? 64u : 128u);
     CUtensorMap ta, tb;
     {
         const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
@@ -300,6 +305,7 @@ int gemm_f16_f32_on(const DeviceInfo* dev, const void* A, const void* B, float* 
     }
     if (plan == TC_GEMM_TILE_PAIR_512x256) return launch_gemm_pair_tall(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
     if (use_pair) return launch_gemm_pair(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
+    if (plan == TC_GEMM_TILE_128x64) return launch_gemm<64, 8>(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
     if (plan == TC_GEMM_TILE_128x128) return launch_gemm<128, 6>(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
     return launch_gemm<256, 4>(ta, tb, C, (int)M, (int)N, (int)K, ldc, dev, stream, extra);
 }
