@@ -307,7 +307,7 @@ static int encode_weights(LstmWeights* lw, const DeviceInfo* dev, const void* W,
 
 template <int HT>
 static int launch_lstm(const CUtensorMap& tx, const LstmWeights& lw, const CUtensorMap& th, const LstmParams& p,
-                       const DeviceInfo* dev, cudaStream_t stream) {
+                       const DeviceInfo* dev, cudaStream_t stream, bool overlap) {
     using Cfg = LstmCfg<HT>;
     auto kernel = lstm_cell_kernel<HT>;
     static bool configured[64] = {};
@@ -325,14 +325,17 @@ static int launch_lstm(const CUtensorMap& tx, const LstmWeights& lw, const CUten
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    // The epilogue warps read the hoisted input projections before they wait for the previous launch. That is
+    // sound behind another step of the same chain, which never writes them, but not behind the GEMM that
+    // produces them and releases its dependents early: the first step of a chain is an ordinary launch.
+    cfg.numAttrs = overlap ? 1 : 0;
     TCB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tx, lw.w, th, lw.u, p));
     return TC_OK;
 }
 
 static int lstm_step(const LstmWeights& lw, const float* gx, const float* bias, const void* x, const void* h_prev,
                      const float* c_prev, void* h_out, float* c_out, int64_t batch, int64_t input, int64_t hidden,
-                     const DeviceInfo* dev, cudaStream_t stream) {
+                     const DeviceInfo* dev, cudaStream_t stream, bool follows_own_step) {
     CUtensorMap tx, th;
     if (int rc = encode_2d(&tx, x, batch, input, kLstmBM)) return rc;
     if (int rc = encode_2d(&th, h_prev, batch, hidden, kLstmBM)) return rc;
@@ -346,7 +349,9 @@ static int lstm_step(const LstmWeights& lw, const float* gx, const float* bias, 
     p.input = static_cast<int>(input);
     p.hidden = static_cast<int>(hidden);
     p.status = dev->status_word;
-    return lw.ht == 16 ? launch_lstm<16>(tx, lw, th, p, dev, stream) : launch_lstm<32>(tx, lw, th, p, dev, stream);
+    // without hoisted projections the kernel reads nothing before its dependency wait
+    const bool overlap = follows_own_step || gx == nullptr;
+    return lw.ht == 16 ? launch_lstm<16>(tx, lw, th, p, dev, stream, overlap) : launch_lstm<32>(tx, lw, th, p, dev, stream, overlap);
 }
 
 static int check_lstm(const char* op, const void* W, const void* U, const void* x, const void* h, const float* c,
@@ -375,7 +380,7 @@ extern "C" int tc_lstm_cell_f16(const void* W, const void* U, const float* bias,
     LstmWeights lw;
     if (int rc = encode_weights(&lw, dev, W, U, batch, input, hidden)) return rc;
     return lstm_step(lw, nullptr, bias, x, h_prev, c_prev, h_out, c_out, batch, input, hidden, dev,
-                     static_cast<cudaStream_t>(stream));
+                     static_cast<cudaStream_t>(stream), false);
 }
 
 static int lstm_chain_impl(const void* W, const void* U, const float* bias, const void* x, const void* h0, const float* c0,
@@ -401,7 +406,7 @@ static int lstm_chain_impl(const void* W, const void* U, const float* bias, cons
         const float* c_prev = t == 0 ? c0 : c_out;
         const float* gx = workspace != nullptr ? workspace + t * batch * 4 * hidden : nullptr;
         if (int rc = lstm_step(lw, gx, bias, xs + t * batch * input, h_prev, c_prev, hs + t * batch * hidden, c_out, batch,
-                               input, hidden, dev, st))
+                               input, hidden, dev, st, t > 0))
             return rc;
     }
     return TC_OK;
@@ -535,7 +540,7 @@ extern "C" int tc_lstm_chain_static_f16(const void* W, const void* U, const floa
         const void* h_prev = t == 0 ? h0 : static_cast<const void*>(hs + (t - 1) * batch * hidden);
         const float* c_prev = t == 0 ? c0 : c_out;
         if (int rc = lstm_step(lw, sd->scratch + t * batch * 4 * hidden, bias, xs + t * batch * input, h_prev, c_prev,
-                               hs + t * batch * hidden, c_out, batch, input, hidden, dev, st))
+                               hs + t * batch * hidden, c_out, batch, input, hidden, dev, st, t > 0))
             return rc;
     }
     return TC_OK;
