@@ -52,6 +52,7 @@ struct LstmParams {
     int batch;
     int input;
     int hidden;
+    int zx, zh;           // step index of this launch's x slab and h_prev slab in their [steps, batch, cols] tensor maps
     uint32_t* status;
 };
 
@@ -131,7 +132,8 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     const int part = from_x ? kb_x : kb_h;
                     const int kcoord = ((from_x ? kbs : kbs - kb_x) + static_cast<int>(blockIdx.x)) % part * kLstmBK;
                     const int slot = stage * Cfg::kSub + sub;
-                    tma_load_2d(smem_a + slot * Cfg::kABytes, from_x ? &tmap_x : &tmap_h, &bar_full[stage], kcoord, b0);
+                    tma_load_3d(smem_a + slot * Cfg::kABytes, from_x ? &tmap_x : &tmap_h, &bar_full[stage], kcoord, b0,
+                                from_x ? p.zx : p.zh);
                     load_b(kbs, slot, &bar_full[stage]);
                 }
                 if (++stage == Cfg::kStages) {
@@ -271,11 +273,13 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     if (threadIdx.x == 0 && *abort_word != 0) atomicMax(p.status, *abort_word);
 }
 
-static int encode_2d(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, uint32_t box_rows) {
-    const uint64_t dims[2] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(rows)};
-    const uint64_t strides[1] = {static_cast<uint64_t>(cols) * 2};
-    const uint32_t box[2] = {kLstmBK, box_rows};
-    return encode_tmap_f16_sw128(out, base, 2, dims, strides, box);
+// Activations of all steps, [steps, batch, cols] dense: one map per chain, the step is the third coordinate of a
+// load (encoding a map per step costs the host more than the launch itself). Rows past `batch` read as zero.
+static int encode_slabs(CUtensorMap* out, const void* base, int64_t steps, int64_t rows, int64_t cols) {
+    const uint64_t dims[3] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(rows), static_cast<uint64_t>(steps)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(cols) * 2, static_cast<uint64_t>(rows) * static_cast<uint64_t>(cols) * 2};
+    const uint32_t box[3] = {kLstmBK, kLstmBM, 1};
+    return encode_tmap_f16_sw128(out, base, 3, dims, strides, box);
 }
 
 struct LstmWeights {
@@ -333,13 +337,12 @@ static int launch_lstm(const CUtensorMap& tx, const LstmWeights& lw, const CUten
     return TC_OK;
 }
 
-static int lstm_step(const LstmWeights& lw, const float* gx, const float* bias, const void* x, const void* h_prev,
-                     const float* c_prev, void* h_out, float* c_out, int64_t batch, int64_t input, int64_t hidden,
-                     const DeviceInfo* dev, cudaStream_t stream, bool follows_own_step) {
-    CUtensorMap tx, th;
-    if (int rc = encode_2d(&tx, x, batch, input, kLstmBM)) return rc;
-    if (int rc = encode_2d(&th, h_prev, batch, hidden, kLstmBM)) return rc;
+static int lstm_step(const LstmWeights& lw, const float* gx, const float* bias, const CUtensorMap& tx, int64_t zx,
+                     const CUtensorMap& th, int64_t zh, const float* c_prev, void* h_out, float* c_out, int64_t batch,
+                     int64_t input, int64_t hidden, const DeviceInfo* dev, cudaStream_t stream, bool follows_own_step) {
     LstmParams p;
+    p.zx = static_cast<int>(zx);
+    p.zh = static_cast<int>(zh);
     p.gx = gx;
     p.bias = bias;
     p.c_prev = c_prev;
@@ -367,6 +370,25 @@ static int check_lstm(const char* op, const void* W, const void* U, const void* 
     return TC_OK;
 }
 
+// The launches of a chain: step t reads x[t] and h[t-1] (h0 for the first) through three tensor maps encoded once.
+// gx_all: [steps, batch, 4*hidden] hoisted input projections, or null.
+static int lstm_chain_steps(const LstmWeights& lw, const float* gx_all, const float* bias, const void* x, const void* h0,
+                            const float* c0, void* h_all, float* c_out, int64_t steps, int64_t batch, int64_t input,
+                            int64_t hidden, const DeviceInfo* dev, cudaStream_t st) {
+    CUtensorMap tx, th0, th;
+    if (int rc = encode_slabs(&tx, x, steps, batch, input)) return rc;
+    if (int rc = encode_slabs(&th0, h0, 1, batch, hidden)) return rc;
+    if (int rc = encode_slabs(&th, h_all, steps, batch, hidden)) return rc;
+    __half* hs = static_cast<__half*>(h_all);
+    for (int64_t t = 0; t < steps; ++t) {
+        const float* gx = gx_all != nullptr ? gx_all + t * batch * 4 * hidden : nullptr;
+        if (int rc = lstm_step(lw, gx, bias, tx, t, t == 0 ? th0 : th, t == 0 ? 0 : t - 1, t == 0 ? c0 : c_out,
+                               hs + t * batch * hidden, c_out, batch, input, hidden, dev, st, t > 0))
+            return rc;
+    }
+    return TC_OK;
+}
+
 }  // namespace tcb
 
 extern "C" int tc_lstm_cell_f16(const void* W, const void* U, const float* bias, const void* x, const void* h_prev,
@@ -379,7 +401,10 @@ extern "C" int tc_lstm_cell_f16(const void* W, const void* U, const float* bias,
     if (int rc = current_device(&dev)) return rc;
     LstmWeights lw;
     if (int rc = encode_weights(&lw, dev, W, U, batch, input, hidden)) return rc;
-    return lstm_step(lw, nullptr, bias, x, h_prev, c_prev, h_out, c_out, batch, input, hidden, dev,
+    CUtensorMap tx, th;
+    if (int rc = encode_slabs(&tx, x, 1, batch, input)) return rc;
+    if (int rc = encode_slabs(&th, h_prev, 1, batch, hidden)) return rc;
+    return lstm_step(lw, nullptr, bias, tx, 0, th, 0, c_prev, h_out, c_out, batch, input, hidden, dev,
                      static_cast<cudaStream_t>(stream), false);
 }
 
@@ -399,17 +424,7 @@ static int lstm_chain_impl(const void* W, const void* U, const float* bias, cons
         // ([steps*batch, input] x [input, 4*hidden], fp32 result) and each step adds its slab in the epilogue.
         if (int rc = tc_gemm_f16_f32(x, W, workspace, steps * batch, 4 * hidden, input, input, input, 4 * hidden, st)) return rc;
     }
-    const __half* xs = static_cast<const __half*>(x);
-    __half* hs = static_cast<__half*>(h_all);
-    for (int64_t t = 0; t < steps; ++t) {
-        const void* h_prev = t == 0 ? h0 : static_cast<const void*>(hs + (t - 1) * batch * hidden);
-        const float* c_prev = t == 0 ? c0 : c_out;
-        const float* gx = workspace != nullptr ? workspace + t * batch * 4 * hidden : nullptr;
-        if (int rc = lstm_step(lw, gx, bias, xs + t * batch * input, h_prev, c_prev, hs + t * batch * hidden, c_out, batch,
-                               input, hidden, dev, st, t > 0))
-            return rc;
-    }
-    return TC_OK;
+    return lstm_chain_steps(lw, workspace, bias, x, h0, c0, h_all, c_out, steps, batch, input, hidden, dev, st);
 }
 
 extern "C" int tc_lstm_chain_f16(const void* W, const void* U, const float* bias, const void* x, const void* h0,
@@ -534,14 +549,5 @@ extern "C" int tc_lstm_chain_static_f16(const void* W, const void* U, const floa
     if (int rc = encode_weights(&lw, dev, W, U, batch, input, hidden)) return rc;
     // The GEMM overwrites every float of the scratch region the steps read, so nothing has to be cleared.
     if (int rc = gemm_f16_f32_on(dev, x, W, sd->scratch, steps * batch, 4 * hidden, input, input, input, 4 * hidden, st, false)) return rc;
-    const __half* xs = static_cast<const __half*>(x);
-    __half* hs = static_cast<__half*>(h_all);
-    for (int64_t t = 0; t < steps; ++t) {
-        const void* h_prev = t == 0 ? h0 : static_cast<const void*>(hs + (t - 1) * batch * hidden);
-        const float* c_prev = t == 0 ? c0 : c_out;
-        if (int rc = lstm_step(lw, sd->scratch + t * batch * 4 * hidden, bias, xs + t * batch * input, h_prev, c_prev,
-                               hs + t * batch * hidden, c_out, batch, input, hidden, dev, st, t > 0))
-            return rc;
-    }
-    return TC_OK;
+    return lstm_chain_steps(lw, sd->scratch, bias, x, h0, c0, h_all, c_out, steps, batch, input, hidden, dev, st);
 }
