@@ -31,5 +31,5 @@ def test_barrier_waits_between_short_mmas_are_exposed_and_wide_mmas_hide_them():
     assert cycles[(64, 4, "try_wait")] >= cycles[(64, 4, "nothing")] + 100
     assert cycles[(128, 4, "ring")] >= cycles[(128, 4, "nothing")] + 100
     # the cost is per wait, so longer groups amortise it, and 128-cycle MMAs hide it
-    assert cycles[(64, 16, "try_wait")] / 16 < cycles[(64, 4, "try_wait")] / 4 * 0.7
+    assert cycles[(64, 16, "try_wait")] / 16 < cycles[(64, 4, "try_wait")] / 4 * 0.8
     assert cycles[(256, 4, "ring")] <= cycles[(256, 4, "nothing")] * 1.1
