@@ -276,7 +276,10 @@ def test_lstm_cell_golden_torch(cuda_ops, clean_status, golden_dir):
 
 
 @pytest.mark.parametrize("batch,inp,hidden,bias", [(128, 64, 16, True), (100, 72, 48, True), (256, 1024, 1024, False),
-                                                    (256, 256, 4096, True), (1, 8, 16, False)])
+                                                    (256, 256, 4096, True), (1, 8, 16, False),
+                                                    # odd numbers of 64-wide K blocks (ring stages hold two): 3 + 7 with
+                                                    # 16-unit tiles, 2 + 75 with 32-unit tiles
+                                                    (200, 192, 448, True), (64, 128, 4800, False)])
 def test_lstm_cell_matches_oracle(cuda_ops, clean_status, batch, inp, hidden, bias):
     w, u, b, x, _, _ = oracle.lstm_inputs(1, batch, inp, hidden, with_bias=bias)
     g = torch.Generator().manual_seed(7)
@@ -309,7 +312,8 @@ def test_lstm_chain_configuration_c4(cuda_ops, clean_status):
         h_prev, c_prev = h1, c1
 
 
-@pytest.mark.parametrize("steps,batch,inp,hidden,bias", [(5, 100, 72, 48, True), (64, 256, 1024, 1024, False)])
+@pytest.mark.parametrize("steps,batch,inp,hidden,bias", [(5, 100, 72, 48, True), (64, 256, 1024, 1024, False),
+                                                          (3, 130, 136, 448, True)])
 def test_lstm_chain_with_workspace_matches_oracle_and_plain_chain(cuda_ops, clean_status, steps, batch, inp, hidden, bias):
     """The chain that hoists x W^T of all steps into one GEMM (caller-provided scratch) against the oracle and
     against the chain without scratch."""
