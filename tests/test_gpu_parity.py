@@ -31,6 +31,8 @@ GEMM_SHAPES = [
         (2304, 2304, 64), (2250, 2300, 136), (4100, 2310, 328),  # enough 256x256 tiles for the CTA-pair kernel, ragged edges
         (128, 19200, 256), (100, 19210, 264),    # one row tile, very wide: the lone 128x256 tiles
         (300, 520, 4096), (1536, 1536, 1536),    # few pair tiles with a long K loop
+        (1290, 1410, 136),                       # lone 128x128 tiles with ragged edges
+        (4000, 4090, 520),                       # 256 pair tiles on 74 pairs: three full waves and a partial one
     ]
 
 
