@@ -160,16 +160,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                                          (kb | k) != 0);
                     }
                     // the stage is free in both CTAs once these MMAs have read it
-                    umma_commit_pair(smem_u32(&bar_empty[stage]));
-                    umma_commit_pair(map_to_cta(smem_u32(&bar_empty[stage]), 1));
+                    umma_commit_pair_both(smem_u32(&bar_empty[stage]));
                     if (++stage == kPairStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (!ok) break;
-                umma_commit_pair(smem_u32(&bar_acc_full[acc]));
-                umma_commit_pair(map_to_cta(smem_u32(&bar_acc_full[acc]), 1));
+                umma_commit_pair_both(smem_u32(&bar_acc_full[acc]));
                 if (++acc == 2) {
                     acc = 0;
                     acc_phase ^= 1u;
@@ -226,6 +224,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 // part of the epilogue is about one percent of a tile.
 constexpr int kTallBK = 64;
 constexpr int kTallStages = 4;
+#ifndef TC_TALL_ROUND
+#define TC_TALL_ROUND 2
+#endif
+constexpr int kTallRound = TC_TALL_ROUND;   // K blocks issued per barrier round (<= kTallStages)
 constexpr int kTallABytes = 2 * kPairBM * kTallBK * 2;          // 256 rows
 constexpr int kTallBBytes = (kPairBN / 2) * kTallBK * 2;        // 128 of the 256 B rows
 constexpr int kTallStageBytes = kTallABytes + kTallBBytes;
@@ -323,41 +325,59 @@ gemm_pair_tall_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             uint32_t phase = 0;
             uint32_t tile_phase = 0;
             bool ok = true;
-            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
-                for (int kb = 0; ok && kb < k_blocks; ++kb) {
-                    if (!mbar_wait(&bar_full[stage], phase, abort_word, kDevTimeoutMma)) {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after_sync();
-                    const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (kTallABytes >> 4);
-                    const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (kTallBBytes >> 4);
+            // MMAs of one K block: both accumulator halves, then the stage is released in both CTAs.
+            auto issue_block = [&](int kb) -> bool {
+                const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (kTallABytes >> 4);
+                const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (kTallBBytes >> 4);
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        if (kb == 0) {   // the epilogue of the previous tile has drained this half
-                            if (!mbar_wait(&bar_acc_empty[half], tile_phase ^ 1u, abort_word, kDevTimeoutMma)) {
+                for (int half = 0; half < 2; ++half) {
+                    if (kb == 0) {   // the epilogue of the previous tile has drained this half
+                        if (!mbar_wait(&bar_acc_empty[half], tile_phase ^ 1u, abort_word, kDevTimeoutMma)) return false;
+                        tc_fence_after_sync();
+                    }
+                    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(half * kPairBN);
+                    const uint32_t a_half = a_lo + static_cast<uint32_t>(half * ((kPairBM * 128) >> 4));
+#pragma unroll
+                    for (int k = 0; k < kTallBK / 16; ++k)
+                        umma_f16_ss_pair(d_tmem, smem_desc_join(a_half + static_cast<uint32_t>(k * 2), desc_hi),
+                                         smem_desc_join(b_lo + static_cast<uint32_t>(k * 2), desc_hi), idesc, (kb | k) != 0);
+                    if (kb == k_blocks - 1) {
+                        umma_commit_pair_both(smem_u32(&bar_acc_full[half]));
+                    }
+                }
+                umma_commit_pair_both(smem_u32(&bar_empty[stage]));
+                if (++stage == kTallStages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+                return true;
+            };
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                // kTallRound K blocks per round: the barriers of the later ones are polled together with the wait for
+                // the first (their latencies overlap), so that a round of up to 8 * kTallRound MMAs pays the issuing
+                // thread's barrier latency once; a block whose poll failed is awaited on its own.
+                for (int kb = 0; ok && kb < k_blocks; kb += kTallRound) {
+                    bool full[kTallRound] = {};
+#pragma unroll
+                    for (int i = 1; i < kTallRound; ++i) {
+                        const int s2 = stage + i < kTallStages ? stage + i : stage + i - kTallStages;
+                        const uint32_t ph2 = stage + i < kTallStages ? phase : phase ^ 1u;
+                        full[i] = kb + i < k_blocks && mbar_try_wait(&bar_full[s2], ph2);
+                    }
+#pragma unroll
+                    for (int i = 0; i < kTallRound; ++i) {
+                        if (kb + i >= k_blocks) break;
+                        if (!full[i]) {
+                            if (!mbar_wait(&bar_full[stage], phase, abort_word, kDevTimeoutMma)) {
                                 ok = false;
                                 break;
                             }
-                            tc_fence_after_sync();
                         }
-                        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(half * kPairBN);
-                        const uint32_t a_half = a_lo + static_cast<uint32_t>(half * ((kPairBM * 128) >> 4));
-#pragma unroll
-                        for (int k = 0; k < kTallBK / 16; ++k)
-                            umma_f16_ss_pair(d_tmem, smem_desc_join(a_half + static_cast<uint32_t>(k * 2), desc_hi),
-                                             smem_desc_join(b_lo + static_cast<uint32_t>(k * 2), desc_hi), idesc, (kb | k) != 0);
-                        if (kb == k_blocks - 1) {
-                            umma_commit_pair(smem_u32(&bar_acc_full[half]));
-                            umma_commit_pair(map_to_cta(smem_u32(&bar_acc_full[half]), 1));
+                        if (i == 0 || !full[i]) tc_fence_after_sync();
+                        if (!issue_block(kb + i)) {
+                            ok = false;
+                            break;
                         }
-                    }
-                    if (!ok) break;
-                    umma_commit_pair(smem_u32(&bar_empty[stage]));
-                    umma_commit_pair(map_to_cta(smem_u32(&bar_empty[stage]), 1));
-                    if (++stage == kTallStages) {
-                        stage = 0;
-                        phase ^= 1u;
                     }
                 }
                 tile_phase ^= 1u;

@@ -288,6 +288,15 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
                  : "memory");
 }
 
+// The same arrival on the barrier at this shared-memory offset in BOTH CTAs of the pair with one instruction
+// (a commit multicast; no data is loaded).
+__device__ __forceinline__ void umma_commit_pair_both(uint32_t bar_cta_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                     bar_cta_addr),
+                 "h"(static_cast<uint16_t>(3))
+                 : "memory");
+}
+
 // ---- tcgen05: TMEM allocation ---------------------------------------------------------------------
 // Executed by one whole warp. `cols` is a power of two in [32, 512]. The base address lands in *slot.
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
