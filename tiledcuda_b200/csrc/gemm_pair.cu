@@ -144,26 +144,36 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 if (!mbar_wait(&bar_acc_empty[acc], acc_phase ^ 1u, abort_word, kDevTimeoutMma)) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kPairBN);
-                for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait(&bar_full[stage], phase, abort_word, kDevTimeoutMma)) {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after_sync();
-                    const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (kPairABytes >> 4);
-                    const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (kPairBBytes >> 4);
+                // Two K blocks per round: the second stage's barrier is polled together with the wait for the first,
+                // so that sixteen MMAs pay the issuing thread's barrier latency once.
+                for (int kb = 0; ok && kb < k_blocks; kb += 2) {
+                    const bool two = kb + 1 < k_blocks;
+                    const int stage2 = stage + 1 == kPairStages ? 0 : stage + 1;
+                    const uint32_t phase2 = stage + 1 == kPairStages ? phase ^ 1u : phase;
+                    const bool second_full = two && mbar_try_wait(&bar_full[stage2], phase2);
+                    for (int i = 0; i < (two ? 2 : 1); ++i) {
+                        if (i == 0 || !second_full) {
+                            if (!mbar_wait(&bar_full[stage], phase, abort_word, kDevTimeoutMma)) {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                        }
+                        const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (kPairABytes >> 4);
+                        const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (kPairBBytes >> 4);
 #pragma unroll
-                    for (int k = 0; k < kPairBK / 16; ++k) {
-                        const uint32_t off_a = static_cast<uint32_t>(((k >> 2) * (kPairBM * 128) + (k & 3) * 32) >> 4);
-                        const uint32_t off_b = static_cast<uint32_t>(((k >> 2) * ((kPairBN / 2) * 128) + (k & 3) * 32) >> 4);
-                        umma_f16_ss_pair(d_tmem, smem_desc_join(a_lo + off_a, desc_hi), smem_desc_join(b_lo + off_b, desc_hi), idesc,
-                                         (kb | k) != 0);
-                    }
-                    // the stage is free in both CTAs once these MMAs have read it
-                    umma_commit_pair_both(smem_u32(&bar_empty[stage]));
-                    if (++stage == kPairStages) {
-                        stage = 0;
-                        phase ^= 1u;
+                        for (int k = 0; k < kPairBK / 16; ++k) {
+                            const uint32_t off_a = static_cast<uint32_t>(((k >> 2) * (kPairBM * 128) + (k & 3) * 32) >> 4);
+                            const uint32_t off_b = static_cast<uint32_t>(((k >> 2) * ((kPairBN / 2) * 128) + (k & 3) * 32) >> 4);
+                            umma_f16_ss_pair(d_tmem, smem_desc_join(a_lo + off_a, desc_hi), smem_desc_join(b_lo + off_b, desc_hi), idesc,
+                                             (kb | i | k) != 0);
+                        }
+                        // the stage is free in both CTAs once these MMAs have read it
+                        umma_commit_pair_both(smem_u32(&bar_empty[stage]));
+                        if (++stage == kPairStages) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
                     }
                 }
                 if (!ok) break;
