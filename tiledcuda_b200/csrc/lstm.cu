@@ -53,6 +53,8 @@ struct LstmParams {
     int input;
     int hidden;
     int zx, zh;           // step index of this launch's x slab and h_prev slab in their [steps, batch, cols] tensor maps
+    int early_reads;      // the launch before this one in the stream is a step of the same chain: nothing it writes
+                          // (h, c) is read by the prefetch of projections and bias, which may then precede the wait
     uint32_t* status;
 };
 
@@ -195,23 +197,30 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         // and the stores are left behind the last MMA.
         float4 pre[16];
         const bool row_ok = row < p.batch && j0 < p.hidden;
+        auto prefetch = [&]() {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) pre[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (row_ok && p.gx != nullptr) {
-            const float* g = p.gx + static_cast<int64_t>(row) * (4 * p.hidden) + j0;
+            for (int i = 0; i < 16; ++i) pre[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row_ok && p.gx != nullptr) {
+                const float* g = p.gx + static_cast<int64_t>(row) * (4 * p.hidden) + j0;
 #pragma unroll
-            for (int gate = 0; gate < 4; ++gate)
+                for (int gate = 0; gate < 4; ++gate)
 #pragma unroll
-                for (int q = 0; q < 4; ++q) pre[gate * 4 + q] = __ldg(reinterpret_cast<const float4*>(g + gate * p.hidden) + q);
-        }
-        if (row_ok && p.bias != nullptr) {
+                    for (int q = 0; q < 4; ++q) pre[gate * 4 + q] = __ldg(reinterpret_cast<const float4*>(g + gate * p.hidden) + q);
+            }
+            if (row_ok && p.bias != nullptr) {
 #pragma unroll
-            for (int gate = 0; gate < 4; ++gate)
+                for (int gate = 0; gate < 4; ++gate)
 #pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    reinterpret_cast<float*>(&pre[gate * 4])[i] += __ldg(p.bias + gate * p.hidden + j0 + i);
-        }
+                    for (int i = 0; i < 16; ++i)
+                        reinterpret_cast<float*>(&pre[gate * 4])[i] += __ldg(p.bias + gate * p.hidden + j0 + i);
+            }
+        };
+        // Behind another step of the same chain the prefetch runs before the dependency wait (that step writes
+        // neither array); behind anything else (the GEMM that produces the projections, a caller's kernel that
+        // may produce the bias) it runs after it, still under the K loop.
+        if (p.early_reads != 0) prefetch();
         grid_dependency_wait();
+        if (p.early_reads == 0) prefetch();
         float4 c_first[4];
         if (row_ok) {
             const float4* c = reinterpret_cast<const float4*>(p.c_prev + static_cast<int64_t>(row) * p.hidden + j0);
@@ -336,7 +345,7 @@ static int encode_weights(LstmWeights* lw, const DeviceInfo* dev, const void* W,
 
 template <int HT>
 static int launch_lstm(const CUtensorMap& tx, const LstmWeights& lw, const CUtensorMap& th, const LstmParams& p,
-                       const DeviceInfo* dev, cudaStream_t stream, bool overlap) {
+                       const DeviceInfo* dev, cudaStream_t stream) {
     using Cfg = LstmCfg<HT>;
     auto kernel = lstm_cell_kernel<HT>;
     static bool configured[64] = {};
@@ -354,10 +363,7 @@ static int launch_lstm(const CUtensorMap& tx, const LstmWeights& lw, const CUten
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    // The epilogue warps read the hoisted input projections before they wait for the previous launch. That is
-    // sound behind another step of the same chain, which never writes them, but not behind the GEMM that
-    // produces them and releases its dependents early: the first step of a chain is an ordinary launch.
-    cfg.numAttrs = overlap ? 1 : 0;
+    cfg.numAttrs = 1;
     TCB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tx, lw.w, th, lw.u, p));
     return TC_OK;
 }
@@ -377,9 +383,8 @@ static int lstm_step(const LstmWeights& lw, const float* gx, const float* bias, 
     p.input = static_cast<int>(input);
     p.hidden = static_cast<int>(hidden);
     p.status = dev->status_word;
-    // without hoisted projections the kernel reads nothing before its dependency wait
-    const bool overlap = follows_own_step || gx == nullptr;
-    return lw.ht == 16 ? launch_lstm<16>(tx, lw, th, p, dev, stream, overlap) : launch_lstm<32>(tx, lw, th, p, dev, stream, overlap);
+    p.early_reads = follows_own_step ? 1 : 0;
+    return lw.ht == 16 ? launch_lstm<16>(tx, lw, th, p, dev, stream) : launch_lstm<32>(tx, lw, th, p, dev, stream);
 }
 
 static int check_lstm(const char* op, const void* W, const void* U, const void* x, const void* h, const float* c,
