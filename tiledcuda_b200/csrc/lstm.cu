@@ -110,7 +110,6 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    grid_launch_dependents();  // the next step's CTAs may start their own set-up as SMs free up
 
     if (warp == 0) {
         if (lane == 0) {
@@ -130,6 +129,11 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             // h_prev (and c_prev, read by the epilogue) come from the previous launch in the stream: with
             // programmatic dependent launch everything above overlapped its tail, the data is awaited here.
             grid_dependency_wait();
+            // Only now may the next step's CTAs start (as SMs free up): they prefetch the hoisted projections before
+            // their own wait, which is sound only once everything older than this step, the GEMM that wrote the
+            // projections included, has completed. Released before this wait, they could start while that GEMM,
+            // which releases its own dependents early, is still running.
+            grid_launch_dependents();
             for (int kb = 0; kb < k_blocks; kb += Cfg::kSub) {
                 if (!mbar_wait(&bar_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) break;
                 const int subs = min(Cfg::kSub, k_blocks - kb);
