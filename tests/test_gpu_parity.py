@@ -106,6 +106,29 @@ def test_gemm_tall_pair_tiles_ragged_and_linear(cuda_ops, clean_status):
     assert torch.equal(c1, c2)
 
 
+@pytest.mark.gpu
+def test_gemm_launches_queued_back_to_back_keep_stream_order(cuda_ops, clean_status):
+    """The GEMM kernels release the launch behind them early and start early themselves (programmatic stream
+    serialization); memory effects must still follow stream order. The second GEMM writes its result over the
+    first one's A operand, the third reads what the second wrote: neither may happen before its predecessor ends."""
+    m, k = 2048, 2048
+    a, b = oracle.gemm_inputs(m, 1024, k)
+    a_dev, b_dev = a.to(DEV), b.to(DEV)
+    c1 = torch.empty(m, 1024, device=DEV)
+    a2, b2 = oracle.gemm_inputs(m, k // 2, 64, seed=5)
+    a2_dev, b2_dev = a2.to(DEV), b2.to(DEV)
+    c2_over_a = a_dev.view(torch.float32)            # [m, k / 2] fp32 on the bytes of A
+    c3 = torch.empty(m, k // 2, device=DEV)
+    for _ in range(3):
+        a_dev.copy_(a)
+        cuda_ops.gemm(a_dev, b_dev, c1)               # reads A ...
+        cuda_ops.gemm(a2_dev, b2_dev, c2_over_a)      # ... which this one overwrites
+        cuda_ops.gemm(a2_dev, b2_dev, c3)
+        torch.cuda.synchronize()
+        assert oracle.within_tolerance(c1, oracle.gemm(a, b))
+        assert torch.equal(c2_over_a, c3)
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 300, 136), (1024, 1024, 1024), (2250, 2300, 136)])
 def test_gemm_bf16_inputs(cuda_ops, clean_status, m, n, k):
     """bf16 operands through the same kernels (all three tile variants): exact products, fp32 accumulation."""
