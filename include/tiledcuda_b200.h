@@ -90,7 +90,8 @@ int tc_b2b_gemm_f16(const void* A, const void* B, const void* D, void* E, int64_
  * V is [batch,heads,seq_kv,head_dim_v] when v_is_transposed == 0, or V^T
  * [batch,heads,head_dim_v,seq_kv] (the layout the reference's Python wrapper produces) otherwise.
  * lse (fp32 [batch,heads,seq_q], natural log of the softmax denominator) may be NULL.
- * Softmax statistics are fp32. Needs head_dim, head_dim_v multiples of 16 and <= 128; seq_kv % 8 == 0.
+ * Softmax statistics are fp32. Needs head_dim, head_dim_v multiples of 16 and <= 128; seq_kv % 8 == 0 when V is
+ * transposed (rows of V^T are 16-byte granular); scale finite, and non-zero when seq_q > 128 and seq_kv % 64 != 0.
  * Replaces `flash_attention` / `run_flash_attention` / `custom_flash_attention_op`
  * (src/kernels/flash_attn.cu:134-312, 314-422, 424-456); the reference fixes scale = 1. */
 int tc_flash_attn_fwd_f16(const void* Q, const void* K, const void* V, void* O, float* lse, int64_t batch,
@@ -147,7 +148,9 @@ int tc_lstm_chain_ws_f16(const void* W, const void* U, const float* bias, const 
  * every GPU that loads the library holds those 64 MiB until the library is unloaded. All calls on one
  * device share that array: calls whose kernels overlap on the GPU (different streams, or the same
  * stream from two threads) race on it; run them one after the other. The first call on a device looks
- * up the array's device address; make that first call before any stream capture begins. A call with
+ * up the array's device address, and the first call with a given shape class (batch above or below 128
+ * rows per tile, hidden size, the tile plan of the hoisted GEMM) sets the shared-memory limits of the
+ * kernels it picks; make a first call with the shapes you will use before any stream capture begins. A call with
  * steps == 0 launches nothing: it synchronises the device and returns TC_ERR_DEVICE if a kernel of an
  * earlier call of this entry point recorded a timeout (tc_device_status() does not cover this path).
  * Arguments otherwise as tc_lstm_chain_f16. It has no counterpart in the reference. */

@@ -4,6 +4,7 @@
 // test_g2s_load.cu, test_swizzled_copy.cu, test_softmax.cu, test_reduce.cu, test_broadcast.cu), whose
 // shapes the Python tests replay. Results are copied back and compared on the host: nothing here asserts
 // or traps on the device. A kernel that gives up on a bounded wait writes 1 to *status.
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -114,6 +115,156 @@ __global__ void k_tile_gemm(const __half* dA, const __half* dB, float* dC, int* 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (threadIdx.x < 32) copy::TmemAllocator::free(acc.address(), tmem_alloc_columns(N));
+}
+
+// The same product with the K slab of each global chunk (TK wide) multiplied in narrower steps of RK through two
+// STileIterators, the loop of the reference's GEMM example (examples/cpp/01_gemm/02_gemm_all_mem/gemm.hpp:145-150:
+// `for k2: load_rA(sAs(k2)); load_rB(sBs(k2)); gemm(rA, rB, acc)`); here the chunks are MMA operands as they are.
+template <int M, int N, int K, int TK, int RK, bool kSwizzled>
+__global__ void k_tile_gemm_siter(const __half* dA, const __half* dB, float* dC, int* status) {
+    extern __shared__ uint8_t raw[];
+    using GlobalA = GlobalTile<__half, tl::RowMajor<M, K>>;
+    using GlobalB = GlobalTile<__half, tl::ColMajor<K, N>>;
+    using GlobalC = GlobalTile<float, tl::RowMajor<M, N>>;
+    using IterA = GTileIterator<GlobalA, TileShape<M, TK>>;
+    using IterB = GTileIterator<GlobalB, TileShape<TK, N>>;
+    using SharedA = SharedTile<__half, tl::RowMajor<M, TK>, kSwizzled>;
+    using SharedB = SharedTile<__half, tl::ColMajor<TK, N>, kSwizzled>;
+    using SIterA = STileIterator<SharedA, TileShape<M, RK>>;
+    using SIterB = STileIterator<SharedB, TileShape<RK, N>>;
+    using Acc = TmemTile<float, tl::RowMajor<128, N>>;
+    using RegC = RowFragment<float, N>;
+    static_assert(TK > RK && SIterA::sc1 == TK / RK && SIterB::sc0 == TK / RK, "the shared slab is walked in TK / RK steps");
+
+    uint8_t* smem = align1024(raw);
+    SharedA sA(reinterpret_cast<__half*>(smem));
+    SharedB sB(reinterpret_cast<__half*>(smem + 64 * 1024));
+    uint64_t* bar_mem = reinterpret_cast<uint64_t*>(smem + 128 * 1024);
+    uint32_t* slot = reinterpret_cast<uint32_t*>(bar_mem + 1);
+
+    MmaBarrier bar(bar_mem);
+    if (threadIdx.x == 0) bar.init();
+    if (threadIdx.x < 32) copy::TmemAllocator::alloc(slot, tmem_alloc_columns(N));
+    __syncthreads();
+    Acc acc(*slot);
+
+    IterA gAs(dA);
+    IterB gBs(dB);
+    SIterA sAs(sA);
+    SIterB sBs(sB);
+    copy::GlobalToSharedLoader<SharedA, WarpLayout> load_a;
+    copy::GlobalToSharedLoader<SharedB, WarpLayout> load_b;
+    bool ok = true;
+    for (int k = 0; k < IterA::sc1; ++k) {
+        load_a(gAs(k), sA);
+        load_b(gBs(k), sB);
+        __copy_async();
+        __syncthreads();
+        for (int k2 = 0; k2 < SIterA::sc1; ++k2) compute::gemm(sAs(k2), sBs(k2), acc, (k | k2) != 0);
+        if (threadIdx.x == 0) bar.commit();
+        ok = bar.wait() && ok;
+    }
+    if (ok) {
+        RegC rC;
+        copy::TmemToRegLoader<Acc, RegC>{}(acc, rC);
+        GlobalC gC(dC);
+        copy::RegToGlobalStorer<GlobalC, RegC, WarpLayout>{}(rC, gC);
+    } else if (threadIdx.x == 0) {
+        *status = 1;
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x < 32) copy::TmemAllocator::free(acc.address(), tmem_alloc_columns(N));
+}
+
+// ------------------------------------------------------------------------------------ loaders and storers
+// global -> shared operand tile -> SharedToRegLoader (one row per thread, converted to Out) -> global.
+template <typename Out, int R, int C, bool kSwizzled>
+__global__ void k_shared_to_reg(const __half* in, Out* out) {
+    extern __shared__ uint8_t raw[];
+    using GlobalIn = GlobalTile<__half, tl::RowMajor<R, C>>;
+    using GlobalOut = GlobalTile<Out, tl::RowMajor<R, C>>;
+    using Shared = SharedTile<__half, tl::RowMajor<R, C>, kSwizzled>;
+    using Reg = RowFragment<Out, C>;
+    Shared s(reinterpret_cast<__half*>(align1024(raw)));
+    GlobalIn gin(in);
+    copy::GlobalToSharedLoader<Shared, WarpLayout>{}(gin, s);
+    __copy_async();
+    __syncthreads();
+    Reg r;
+    copy::SharedToRegLoader<Reg, WarpLayout>{}(s, r);
+    GlobalOut gout(out);
+    copy::RegToGlobalStorer<GlobalOut, Reg, WarpLayout>{}(r, gout);
+}
+
+// global fp32 [128, C] -> row fragments -> RegToTmemStorer -> TMEM -> TmemToRegLoader -> global.
+template <int C>
+__global__ void k_tmem_roundtrip(const float* in, float* out) {
+    __shared__ uint32_t slot;
+    using Global = GlobalTile<float, tl::RowMajor<128, C>>;
+    using Reg = RowFragment<float, C>;
+    using Tmem = TmemTile<float, tl::RowMajor<128, C>>;
+    if (threadIdx.x < 32) copy::TmemAllocator::alloc(&slot, tmem_alloc_columns(C));
+    __syncthreads();
+    Tmem t(slot);
+    Global gin(in), gout(out);
+    Reg a, b;
+    copy::GlobalToRegLoader<Reg, WarpLayout>{}(gin, a);
+    copy::RegToTmemStorer<Reg, Tmem>{}(a, t);
+    __syncthreads();
+    copy::TmemToRegLoader<Tmem, Reg>{}(t, b);
+    copy::RegToGlobalStorer<Global, Reg, WarpLayout>{}(b, gout);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x < 32) copy::TmemAllocator::free(t.address(), tmem_alloc_columns(C));
+}
+
+// Tensor-map load of an R x C window at (row0, col0) of a larger fp16 matrix into a swizzled operand tile
+// (TmaTileLoader, one thread), then out through SharedToGlobalStorer. The wait on the copy is bounded.
+template <int R, int C>
+__global__ void k_tma_load(const __grid_constant__ CUtensorMap map, int row0, int col0, __half* out, int* status) {
+    extern __shared__ uint8_t raw[];
+    using Shared = SharedTile<__half, tl::RowMajor<R, C>, true>;
+    using Global = GlobalTile<__half, tl::RowMajor<R, C>>;
+    uint8_t* smem = align1024(raw);
+    Shared s(reinterpret_cast<__half*>(smem));
+    CopyBarrier bar(reinterpret_cast<uint64_t*>(smem + Shared::kBytes));
+    if (threadIdx.x == 0) {
+        bar.init();
+        bar.expect(Shared::kBytes);
+        copy::TmaTileLoader<Shared>{}(&map, s, bar.get(), col0, row0);
+    }
+    __syncthreads();
+    if (bar.wait()) {
+        Global gout(out);
+        copy::SharedToGlobalStorer<Shared, WarpLayout>{}(s, gout);
+    } else if (threadIdx.x == 0) {
+        *status = 1;
+    }
+}
+
+// ------------------------------------------------------------------------------------ a wait that runs out
+// One CTA allocates TMEM and waits, with a limit of `limit_ns`, on an MMA barrier that nothing ever commits. The
+// wait gives up, every thread sees `false`, the CTA frees its TMEM, records status 1 and returns: the way every
+// kernel of the library leaves when a wait runs out. The context stays usable; nothing traps.
+__global__ void k_wait_runs_out(unsigned long long limit_ns, int* status, unsigned long long* waited_ns) {
+    __shared__ uint64_t bar_mem;
+    __shared__ uint32_t slot;
+    MmaBarrier bar(&bar_mem);
+    if (threadIdx.x == 0) bar.init();
+    if (threadIdx.x < 32) copy::TmemAllocator::alloc(&slot, 32);
+    __syncthreads();
+    unsigned long long t0, t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    const bool ok = bar.wait(limit_ns);
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    if (threadIdx.x == 0) {
+        *status = ok ? 0 : 1;
+        *waited_ns = t1 - t0;
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x < 32) copy::TmemAllocator::free(slot, 32);
 }
 
 // ------------------------------------------------------------------------------------ fused two GEMMs
@@ -389,6 +540,115 @@ extern "C" int tcx_tile_gemm(int id, const __half* A, const __half* B, float* C,
         GEMM_CASE(42, 64, 128, 128, 64, true)
         default: return -1;
     }
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+#define SGEMM_CASE(id, M, N, K, TK, RK, SWZ)                                              \
+    case id: {                                                                            \
+        auto kern = k_tile_gemm_siter<M, N, K, TK, RK, SWZ>;                              \
+        if (set_smem(kern, 130 * 1024 + 1024)) return -3;                                 \
+        kern<<<1, 128, 130 * 1024 + 1024>>>(A, B, C, status);                             \
+        *m = M; *n = N; *k = K;                                                           \
+        break;                                                                            \
+    }
+
+// GEMMs whose shared K slab (TK) is walked in narrower steps (RK) with STileIterators: (M, N, K, TK, RK, swizzled).
+// The cases cover steps inside one 128-byte swizzle row (RK = 16, 32), steps of whole swizzle rows (RK = 64), the
+// interleaved layout, and M < 128.
+extern "C" int tcx_siter_gemm_case_count() { return 6; }
+extern "C" int tcx_tile_gemm_siter(int id, const __half* A, const __half* B, float* C, int* status, int* m, int* n, int* k) {
+    switch (id) {
+        SGEMM_CASE(0, 64, 256, 256, 64, 16, true)
+        SGEMM_CASE(1, 128, 128, 256, 128, 64, true)
+        SGEMM_CASE(2, 128, 64, 128, 64, 32, true)
+        SGEMM_CASE(3, 64, 64, 128, 64, 16, false)
+        SGEMM_CASE(4, 128, 128, 128, 128, 32, false)
+        SGEMM_CASE(5, 32, 48, 256, 128, 16, true)
+        default: return -1;
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+#define S2R_CASE(id, OUT, R, C, SWZ)                                                      \
+    case id: {                                                                            \
+        auto kern = k_shared_to_reg<OUT, R, C, SWZ>;                                      \
+        if (set_smem(kern, 70 * 1024)) return -3;                                         \
+        kern<<<1, 128, 70 * 1024>>>(in, static_cast<OUT*>(out));                          \
+        *rows = R; *cols = C; *out_elem = sizeof(OUT);                                    \
+        break;                                                                            \
+    }
+
+extern "C" int tcx_shared_to_reg_case_count() { return 6; }
+extern "C" int tcx_shared_to_reg(int id, const __half* in, void* out, int* rows, int* cols, int* out_elem) {
+    switch (id) {
+        S2R_CASE(0, __half, 128, 64, true)
+        S2R_CASE(1, float, 128, 64, true)
+        S2R_CASE(2, __half, 64, 128, false)
+        S2R_CASE(3, float, 96, 32, false)
+        S2R_CASE(4, float, 128, 128, true)
+        S2R_CASE(5, __half, 16, 16, false)
+        default: return -1;
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int tcx_tmem_roundtrip(int cols, const float* in, float* out) {
+    if (cols == 16)
+        k_tmem_roundtrip<16><<<1, 128>>>(in, out);
+    else if (cols == 64)
+        k_tmem_roundtrip<64><<<1, 128>>>(in, out);
+    else if (cols == 128)
+        k_tmem_roundtrip<128><<<1, 128>>>(in, out);
+    else
+        return -1;
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Tensor map of a [rows, cols] fp16 row-major matrix with a box of 64 columns x box_rows rows and 128-byte swizzle,
+// encoded through the runtime's driver entry point (no link-time dependency on the driver library).
+static int encode_map(CUtensorMap* map, const void* base, int rows, int cols, int box_rows) {
+    typedef CUresult (*Fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                           const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                           CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || fn == nullptr) return -4;
+    const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(cols) * 2};
+    const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t estride[2] = {1, 1};
+    const CUresult r = reinterpret_cast<Fn>(fn)(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), gdim, gstride, box,
+                                                estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -5;
+}
+
+#define TMA_CASE(id, R, C)                                                                \
+    case id: {                                                                            \
+        if (int rc = encode_map(&map, in, rows, cols, R)) return rc;                      \
+        auto kern = k_tma_load<R, C>;                                                     \
+        if (set_smem(kern, 70 * 1024)) return -3;                                         \
+        kern<<<1, 128, 70 * 1024>>>(map, row0, col0, out, status);                        \
+        *tile_rows = R; *tile_cols = C;                                                   \
+        break;                                                                            \
+    }
+
+// Loads the tile at (row0, col0) of the [rows, cols] matrix `in`; col0 must be a multiple of 8 (TMA's 16-byte rule).
+extern "C" int tcx_tma_load(int id, const __half* in, int rows, int cols, int row0, int col0, __half* out, int* status,
+                            int* tile_rows, int* tile_cols) {
+    if (col0 % 8 != 0 || row0 < 0 || col0 < 0) return -6;
+    CUtensorMap map;
+    switch (id) {
+        TMA_CASE(0, 64, 64)
+        TMA_CASE(1, 128, 128)
+        TMA_CASE(2, 32, 256)
+        default: return -1;
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int tcx_wait_runs_out(unsigned long long limit_ns, int* status, unsigned long long* waited_ns) {
+    k_wait_runs_out<<<1, 128>>>(limit_ns, status, waited_ns);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -129,7 +129,9 @@ def make_lstm() -> None:
 
 
 if __name__ == "__main__":
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <path of the reference checkout>")
+    ref = Path(sys.argv[1])
     make_flash_attn(ref)
     make_scatter()
     make_gemm_ramp()

@@ -61,6 +61,8 @@ def test_every_declaration_cites_the_reference_or_says_it_has_no_counterpart():
         (lambda l: l.tc_lstm_cell_f16(16, 16, None, 16, 16, 16, 16, 16, 8, 64, 24, None), "multiple of 16"),
         (lambda l: l.tc_lstm_cell_f16(16, 16, None, 16, 32, 16, 32, 16, 8, 64, 32, None), "alias"),
         (lambda l: l.tc_lstm_chain_f16(16, 16, None, 16, 16, 16, 16, 16, 0, 8, 64, 32, None), "steps"),
+        (lambda l: l.tc_lstm_chain_static_f16(16, 16, None, 16, 16, 16, 16, 16, -1, 8, 64, 32, None), "negative"),
+        (lambda l: l.tc_flash_attn_fwd_f16(16, 16, 16, 16, None, 1, 1, 256, 104, 64, 64, 0.0, 0, None), "scale == 0"),
     ],
 )
 def test_bad_arguments_return_a_status_and_a_message(call, needle):
@@ -68,6 +70,16 @@ def test_bad_arguments_return_a_status_and_a_message(call, needle):
     rc = call(lib)
     assert rc == -1  # TC_ERR_BAD_ARG
     assert needle in lib.tc_last_error().decode()
+
+
+def test_static_chain_refuses_sizes_beyond_its_built_in_scratch_without_a_device():
+    """The 64 MiB limit is tested by division: a step count that would wrap steps * batch * 4 * hidden * 4 around
+    2^64 is refused like any other oversize request, before any device is touched."""
+    lib = _lib.load()
+    for steps in (1 << 62, (1 << 64) // (8 * 4 * 32 * 4) + 1, 1 << 40, 16385):
+        rc = lib.tc_lstm_chain_static_f16(16, 16, None, 16, 16, 16, 16, 16, steps % (1 << 63), 8, 64, 32, None)
+        assert rc == -2, steps  # TC_ERR_UNSUPPORTED
+        assert "built into" in lib.tc_last_error().decode()
 
 
 def test_scatter_argument_checks():

@@ -106,6 +106,33 @@ def test_gemm_tall_pair_tiles_ragged_and_linear(cuda_ops, clean_status):
     assert torch.equal(c1, c2)
 
 
+@pytest.mark.parametrize("n", [8192, 16384])
+def test_gemm_headline_sizes_on_the_benchmark_inputs(cuda_ops, clean_status, n):
+    """The benchmark's own configuration: M = N = K = 8192 (the headline) and 16384, uniform[-1, 1) inputs from
+    seed 1234 (oracle.gemm_inputs), through the C ABI. 96 rows are compared with the fp32 oracle: the first, a
+    middle and the last 512-row pair tile, and in each both CTAs of the pair (rows 0-255 / 256-511 of the tile)
+    and both 128-row accumulator halves of each CTA. The rest of the result is covered by a checksum: the column
+    sums of C equal (sum of the rows of A) B^T, computed in float64 from the same inputs."""
+    a, b = oracle.gemm_inputs(n, n, n)
+    a_dev, b_dev = a.to(DEV), b.to(DEV)
+    c = torch.full((n, n), float("nan"), device=DEV)
+    cuda_ops.gemm(a_dev, b_dev, c)
+    torch.cuda.synchronize()
+    rows = []
+    for tile0 in (0, (n // 1024) * 512, n - 512):
+        for quarter in range(4):                       # CTA 0 half 0, CTA 0 half 1, CTA 1 half 0, CTA 1 half 1
+            rows += [tile0 + quarter * 128 + r for r in (0, 17, 38, 59, 64, 85, 106, 127)]
+    rows = torch.tensor(rows)
+    assert rows.numel() == 96
+    got = c[rows.to(DEV)].cpu()
+    assert_close(got, oracle.gemm(a[rows], b), max_abs=2e-3, rel_fro=1e-5)
+    # checksum over every row: sum_i C[i, :] against (sum_i A[i, :]) B^T in float64
+    col_sums = c.double().sum(dim=0).cpu()
+    want = (a.double().sum(dim=0, keepdim=True) @ b.double().t()).view(-1)
+    assert not torch.isnan(col_sums).any()
+    assert (col_sums - want).abs().max().item() <= 2e-3 * math.sqrt(n) * 4
+
+
 @pytest.mark.gpu
 def test_gemm_launches_queued_back_to_back_keep_stream_order(cuda_ops, clean_status):
     """The GEMM kernels release the launch behind them early and start early themselves (programmatic stream

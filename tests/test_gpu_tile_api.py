@@ -154,3 +154,89 @@ def test_row_operations(lib, cols):
     assert torch.allclose(rsum.cpu(), x.sum(dim=1), atol=1e-4)
     assert torch.allclose(centered.cpu(), x - x.max(dim=1, keepdim=True).values, atol=1e-6)
     assert torch.allclose(csum.cpu(), x.view(4, 32, cols).sum(dim=1), atol=1e-4)
+
+
+@pytest.mark.parametrize("case", range(6))
+def test_tile_gemm_over_shared_tile_iterators(lib, case):
+    """compute::gemm on the chunks an STileIterator hands out: the shared K slab of each global chunk is multiplied
+    in narrower steps, the inner loop of the reference's GEMM example
+    (examples/cpp/01_gemm/02_gemm_all_mem/gemm.hpp:145-150)."""
+    assert lib.tcx_siter_gemm_case_count() == 6
+    dims = [(64, 256, 256), (128, 128, 256), (128, 64, 128), (64, 64, 128), (128, 128, 128), (32, 48, 256)][case]
+    M, N, K = dims
+    a, b = oracle.gemm_inputs(M, N, K, seed=400 + case)
+    c = torch.full((M, N), float("nan"), device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    m, n, k = (ctypes.c_int() for _ in range(3))
+    a_dev, b_dev = a.to(DEV), b.to(DEV)
+    assert lib.tcx_tile_gemm_siter(case, _p(a_dev), _p(b_dev), _p(c), _p(status), ctypes.byref(m), ctypes.byref(n), ctypes.byref(k)) == 0
+    torch.cuda.synchronize()
+    assert status.item() == 0 and (m.value, n.value, k.value) == dims
+    ref = oracle.gemm(a, b)
+    assert oracle.max_abs_err(c, ref) <= 1e-3 and oracle.rel_fro_err(c, ref) <= 1e-5, dims
+
+
+@pytest.mark.parametrize("case", range(6))
+def test_shared_to_reg_loader_round_trip(lib, case):
+    """global -> shared operand tile (swizzled or interleaved) -> SharedToRegLoader (one row per thread, fp16 kept or
+    widened to fp32) -> global reproduces the `i % 2048` ramp exactly."""
+    assert lib.tcx_shared_to_reg_case_count() == 6
+    rows, cols, elem = (ctypes.c_int() for _ in range(3))
+    ramp = (torch.arange(128 * 128, device=DEV) % 2048).to(torch.float16)
+    out = torch.full((128 * 128,), -1.0, dtype=torch.float32, device=DEV)
+    assert lib.tcx_shared_to_reg(case, _p(ramp), _p(out), ctypes.byref(rows), ctypes.byref(cols), ctypes.byref(elem)) == 0
+    torch.cuda.synchronize()
+    n = rows.value * cols.value
+    got = out.view(torch.float16)[:n] if elem.value == 2 else out[:n]
+    assert torch.equal(got.float(), ramp[:n].float())
+
+
+@pytest.mark.parametrize("cols", [16, 64, 128])
+def test_reg_to_tmem_storer_round_trip(lib, cols):
+    """row fragments -> RegToTmemStorer -> tensor memory -> TmemToRegLoader -> global is exact."""
+    x = torch.randn(128, cols, generator=torch.Generator().manual_seed(7)).to(DEV)
+    y = torch.full_like(x, float("nan"))
+    assert lib.tcx_tmem_roundtrip(cols, _p(x), _p(y)) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("case,row0,col0", [(0, 0, 0), (0, 64, 128), (1, 128, 64), (2, 32, 0), (1, 200, 192)])
+def test_tma_tile_loader_matches_the_matrix(lib, case, row0, col0):
+    """TmaTileLoader: a tensor map built on the host, one thread issuing the loads into a swizzled operand tile; the
+    tile read back through SharedToGlobalStorer equals the same window of the matrix (what the cp.async loader
+    delivers), with zero fill where the window leaves the matrix."""
+    rows, cols = 256, 320
+    src = (torch.arange(rows * cols, device=DEV) % 2048).to(torch.float16).view(rows, cols)
+    tr, tc = [(64, 64), (128, 128), (32, 256)][case]
+    out = torch.full((tr, tc), -1.0, dtype=torch.float16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    r, c = ctypes.c_int(), ctypes.c_int()
+    assert lib.tcx_tma_load(case, _p(src), rows, cols, row0, col0, _p(out), _p(status), ctypes.byref(r), ctypes.byref(c)) == 0
+    torch.cuda.synchronize()
+    assert status.item() == 0 and (r.value, c.value) == (tr, tc)
+    want = torch.zeros(tr, tc, dtype=torch.float16, device=DEV)
+    rr, cc = min(tr, rows - row0), min(tc, cols - col0)
+    want[:rr, :cc] = src[row0:row0 + rr, col0:col0 + cc]
+    assert torch.equal(out, want)
+
+
+def test_a_wait_that_runs_out_returns_a_status_and_leaves_the_device_usable(lib):
+    """A bounded wait gives up: a CTA waits 2 ms on an MMA barrier that nothing commits, reports status 1, frees its
+    tensor memory and returns (no trap, no endless loop). The next kernel on the same context runs normally."""
+    status = torch.full((1,), -1, dtype=torch.int32, device=DEV)
+    waited = torch.zeros(1, dtype=torch.int64, device=DEV)
+    lib.tcx_wait_runs_out.argtypes = [ctypes.c_ulonglong, ctypes.c_void_p, ctypes.c_void_p]
+    assert lib.tcx_wait_runs_out(2_000_000, _p(status), _p(waited)) == 0
+    torch.cuda.synchronize()
+    assert status.item() == 1
+    assert 2_000_000 <= waited.item() < 200_000_000   # gave up after the limit, and soon after it
+    # the context is intact: a tile GEMM (which allocates the tensor memory the waiting CTA freed) still matches
+    a, b = oracle.gemm_inputs(128, 128, 64, seed=9)
+    c = torch.full((128, 128), float("nan"), device=DEV)
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    m, n, k = (ctypes.c_int() for _ in range(3))
+    a_dev, b_dev = a.to(DEV), b.to(DEV)
+    assert lib.tcx_tile_gemm(12, _p(a_dev), _p(b_dev), _p(c), _p(st), ctypes.byref(m), ctypes.byref(n), ctypes.byref(k)) == 0
+    torch.cuda.synchronize()
+    assert st.item() == 0 and oracle.max_abs_err(c, oracle.gemm(a, b)) <= 1e-3

@@ -88,3 +88,63 @@ def test_errors_surface_as_runtime_errors(ptc):
         ptc.gemm(a, a, torch.zeros(128, 128, device=DEV))
     with pytest.raises((RuntimeError, NotImplementedError)):
         ptc.gemm(a.cpu(), a.cpu(), torch.zeros(128, 128))  # no CPU kernel is registered
+
+
+def test_reference_import_lines_work_unchanged():
+    """`from pytiledcuda import TiledFlashAttention` (tests/python/test_flash_attn.py:6 of the reference) and
+    `pytiledcuda.scatter_nd(data, indices, updates)` (tests/python/test_scatter_nd.py:43) import and run as written."""
+    import pytiledcuda
+    from pytiledcuda import TiledFlashAttention
+
+    g = torch.Generator().manual_seed(1234)                     # the reference test's seed and shapes
+    q = torch.randn(64, 128, generator=g).half().to(DEV)
+    k_t = torch.randn(128, 128, generator=g).half().to(DEV)
+    v = torch.randn(128, 128, generator=g).half().to(DEV)
+    out = TiledFlashAttention(q, k_t, v).forward()
+    ref, _ = oracle.flash_attention(q.cpu(), k_t.cpu().t().contiguous(), v.cpu(), scale=1.0)
+    assert oracle.max_abs_err(out, ref) <= 2e-2
+
+    data = torch.zeros(7, 8, 9, 10, device=DEV)
+    idx = torch.tensor([[0, 1], [6, 7], [3, 3]], dtype=torch.int64, device=DEV)
+    upd = torch.arange(3 * 90, dtype=torch.float32, device=DEV).view(3, 9, 10)
+    pytiledcuda.scatter_nd(data, idx, upd)
+    want = torch.zeros(7, 8, 9, 10)
+    want[idx[:, 0].cpu(), idx[:, 1].cpu()] = upd.cpu()
+    assert torch.equal(data.cpu(), want)
+
+
+def test_wrong_shapes_raise_before_any_launch(ptc, clean_status):
+    """The dispatcher-level ops refuse tensors whose shapes would send a kernel outside its buffers: each call below
+    raises a RuntimeError from the argument checks, nothing is launched, and the device status word stays clean."""
+    f16 = dict(dtype=torch.float16, device=DEV)
+    table = torch.zeros(64, 8, **f16)
+    idx = torch.zeros(10, 1, dtype=torch.int64, device=DEV)
+    with pytest.raises(RuntimeError, match="updates has"):
+        ptc.scatter_nd(table, idx, torch.zeros(9, 8, **f16))          # one slice short
+    with pytest.raises(RuntimeError, match="updates has"):
+        ptc.scatter_nd_add(table.float(), idx, torch.zeros(10, 4, device=DEV))
+    with pytest.raises(RuntimeError, match="do not fit"):
+        ptc.scatter_nd(table, torch.zeros(10, 3, dtype=torch.int64, device=DEV), torch.zeros(10, **f16))
+
+    hidden, inp, batch = 32, 64, 64
+    w, u = torch.zeros(4 * hidden, inp, **f16), torch.zeros(4 * hidden, hidden, **f16)
+    x, h = torch.zeros(batch, inp, **f16), torch.zeros(batch, hidden, **f16)
+    c = torch.zeros(batch, hidden, device=DEV)
+    h_out, c_out = torch.empty_like(h), torch.empty_like(c)
+    with pytest.raises(RuntimeError, match="must be"):
+        ptc.lstm_cell(w, u, None, x, h[: batch // 2], c, h_out, c_out)           # h_prev too short
+    with pytest.raises(RuntimeError, match="must be"):
+        ptc.lstm_cell(w, u, None, x, h, c, h_out, c_out[:, : hidden // 2].contiguous())
+    with pytest.raises(RuntimeError, match="bias must have"):
+        ptc.lstm_cell(w, u, torch.zeros(hidden, device=DEV), x, h, c, h_out, c_out)
+    with pytest.raises(RuntimeError, match="alias"):
+        ptc.lstm_cell(w, u, None, x, h, c, h, c_out)
+    with pytest.raises(RuntimeError, match="2-D"):
+        ptc.lstm_cell(w, u, None, x.view(1, batch, inp), h, c, h_out, c_out)
+    with pytest.raises(RuntimeError, match="weight shape"):
+        ptc.lstm_cell(w, torch.zeros(4 * hidden, hidden + 16, **f16), None, x, h, c, h_out, c_out)
+
+    if torch.cuda.device_count() > 1:
+        a = torch.zeros(128, 64, **f16)
+        with pytest.raises(RuntimeError, match="one device"):
+            ptc.gemm(a, a.to("cuda:1"), torch.zeros(128, 128, device=DEV))

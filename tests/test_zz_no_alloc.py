@@ -8,8 +8,9 @@ workspace in a 64 MiB array inside the library image instead.
 The test goes through the C ABI with ctypes, runs the entry point twice in a row on different inputs
 (the array keeps the first call's contents, which the second call must fully overwrite) and compares each
 result with tc_lstm_chain_ws_f16 on the same inputs: same kernels, same order of operations, so the
-outputs must agree to the bit; the assertion allows the tolerance the other LSTM tests use. It also
-checks the size limit and the steps == 0 status query. The file name sorts after every other test file
+outputs must agree to the bit; the assertion allows the tolerance the other LSTM tests use. Around the
+second problem's calls it reads the free device memory (cudaMemGetInfo) and requires it unchanged: the call
+allocated nothing. It also checks the size limit and the steps == 0 status query. The file name sorts after every other test file
 so that a run that stops at the first failure has already run the rest.
 """
 import ctypes
@@ -26,6 +27,12 @@ STATIC_SCRATCH_BYTES = 64 * 1024 * 1024
 
 def _ptr(t):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _free_device_bytes():
+    """Free device memory as the driver reports it (cudaMemGetInfo), past torch's caching allocator."""
+    free, _total = torch.cuda.mem_get_info(0)
+    return free
 
 
 def _run_static(lib, w, u, bias, x, h0, c0, h_all, c_out):
@@ -65,6 +72,18 @@ def test_static_scratch_chain_matches_the_workspace_chain_twice_in_a_row():
         rc = _run_static(lib, *dev, h_static, c_static)
         assert rc == 0, lib.tc_last_error().decode()
         torch.cuda.synchronize()
+        # The claim in the entry point's name: a call takes no device memory. Free memory as the driver reports it
+        # (cudaMemGetInfo) is read on both sides of a second call with the same shapes; the first call with a shape
+        # class may make the driver load kernels, which is not an allocation of the entry point's.
+        h_first, c_first = h_static.clone(), c_static.clone()   # computed over whatever the previous problem left in the scratch
+        free_before = _free_device_bytes()
+        h_static.fill_(float("nan"))
+        c_static.fill_(float("nan"))
+        rc = _run_static(lib, *dev, h_static, c_static)
+        assert rc == 0, lib.tc_last_error().decode()
+        torch.cuda.synchronize()
+        assert _free_device_bytes() == free_before
+        assert torch.equal(h_first, h_static) and torch.equal(c_first, c_static)
         h_ws = torch.empty_like(h_static)
         c_ws = torch.empty_like(c_static)
         assert _run_workspace(lib, *dev, h_ws, c_ws) == 0, lib.tc_last_error().decode()

@@ -127,16 +127,6 @@ def build_tile_api_tests(force: bool = False) -> list[Path]:
             raise RuntimeError(f"host layout checks failed to build:\n{res.stderr[-6000:]}")
     if host_lib.exists():
         outs.append(host_lib)
-    # the MMA issue-latency microbenchmark: a stand-alone program against csrc/sm100.cuh
-    lat_src, lat_bin = TESTS_CPP / "mma_issue_latency.cu", TESTS_CPP / "mma_issue_latency"
-    csrc_mtime = (PKG / "csrc" / "sm100.cuh").stat().st_mtime
-    if lat_src.exists() and (force or not lat_bin.exists() or lat_bin.stat().st_mtime < max(lat_src.stat().st_mtime, csrc_mtime)):
-        cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", str(lat_src), "-o", str(lat_bin)]
-        res = subprocess.run(cmd, capture_output=True, text=True)
-        if res.returncode != 0:
-            raise RuntimeError(f"mma_issue_latency failed to build:\n{res.stderr[-6000:]}")
-    if lat_bin.exists():
-        outs.append(lat_bin)
     return outs
 
 

@@ -447,18 +447,12 @@ int launch_attn_pingpong(const void* Q, const void* K, const void* V, void* O, f
     p.lse = lse;
     p.status = dev->status_word;
     const dim3 grid(static_cast<unsigned>((seq_q + 2 * kFaBM - 1) / (2 * kFaBM)), static_cast<unsigned>(batch * heads));
-    static bool configured[2][64] = {};
+    static OncePerDevice once[2];
     if (v_trans) {
-        if (!configured[1][dev->device]) {
-            TCB_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFaSmem));
-            configured[1][dev->device] = true;
-        }
+        if (int rc = raise_smem_limit_once(once[1], dev->device, attn_fwd_kernel<true>, kFaSmem)) return rc;
         attn_fwd_kernel<true><<<grid, kFaThreads, kFaSmem, stream>>>(tq, tk, tv, p);
     } else {
-        if (!configured[0][dev->device]) {
-            TCB_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFaSmem));
-            configured[0][dev->device] = true;
-        }
+        if (int rc = raise_smem_limit_once(once[0], dev->device, attn_fwd_kernel<false>, kFaSmem)) return rc;
         attn_fwd_kernel<false><<<grid, kFaThreads, kFaSmem, stream>>>(tq, tk, tv, p);
     }
     TCB_CUDA(cudaGetLastError());

@@ -401,11 +401,8 @@ static int launch_chain(const void* Q, const void* K, const void* V, void* out, 
         if (int rc = encode_3d(&tv, V, batch, inner, dv, kChBN)) return rc;
     }
     auto kernel = chain_kernel<kSoftmax, kVTrans>;
-    static bool configured[64] = {};
-    if (!configured[dev->device]) {
-        TCB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kChSmem));
-        configured[dev->device] = true;
-    }
+    static OncePerDevice once;
+    if (int rc = raise_smem_limit_once(once, dev->device, kernel, kChSmem)) return rc;
     ChainParams p;
     p.rows = static_cast<int>(rows);
     p.inner = static_cast<int>(inner);
@@ -460,7 +457,12 @@ static int attn_entry(const char* op, const void* Q, const void* K, const void* 
     TCB_REQUIRE(isfinite(scale), "%s: scale is not finite", op);
     TCB_REQUIRE(!causal || scale != 0.f, "%s: a causal mask needs a non-zero scale", op);
     auto* st = static_cast<cudaStream_t>(stream);
-    if (seq_q > kChBM || causal || seq_major)
+    const bool two_tiles = seq_q > kChBM || causal || seq_major;
+    // The two-tile kernel masks a score by setting it to the infinity whose product with the scale is -inf, which
+    // has no meaning for scale == 0; it masks whenever the last 64 KV rows are not all there.
+    TCB_REQUIRE(!(two_tiles && scale == 0.f && seq_kv % 64 != 0),
+                "%s: scale == 0 needs seq_kv to be a multiple of 64 for this shape (got %lld)", op, (long long)seq_kv);
+    if (two_tiles)
         return launch_attn_pingpong(Q, K, V, O, lse, batch, heads, seq_q, seq_kv, head_dim, head_dim_v, scale,
                                     v_is_transposed != 0, causal != 0, seq_major != 0, st);
     if (v_is_transposed)

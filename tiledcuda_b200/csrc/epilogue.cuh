@@ -16,8 +16,6 @@ constexpr int kStoreStageBytes = 4 * 2 * 4096;   // per epilogue warp two 32-row
 inline int output_store_map(CUtensorMap* tc, int* use_tma, const float* C, int M, int N, int64_t ldc) {
     memset(tc, 0, sizeof(*tc));
     *use_tma = ((ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15u) == 0) ? 1 : 0;
-    if (const char* e = getenv("TC_GEMM_STORE"))   // "direct": stores from registers (tuning aid)
-        if (e[0] == 'd') *use_tma = 0;
     if (!*use_tma) return TC_OK;
     return encode_tmap_f32_sw128(tc, C, static_cast<uint64_t>(N), static_cast<uint64_t>(M), static_cast<uint64_t>(ldc) * 4, 32, 32);
 }

@@ -223,11 +223,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, float* C, i
                        const DeviceInfo* dev, cudaStream_t stream, uint32_t idesc_extra) {
     using S = GemmSmem<BN, STAGES>;
     auto kernel = gemm_f16_f32_kernel<BN, STAGES>;
-    static bool configured[64] = {};
-    if (!configured[dev->device]) {
-        TCB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
-        configured[dev->device] = true;
-    }
+    static OncePerDevice once;
+    if (int rc = raise_smem_limit_once(once, dev->device, kernel, S::kTotal)) return rc;
     const int tiles_m = (M + kGemmBM - 1) / kGemmBM;
     const int tiles_n = (N + BN - 1) / BN;
     const int tiles = tiles_m * tiles_n;
@@ -283,11 +280,7 @@ int gemm_tile_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
 int gemm_f16_f32_on(const DeviceInfo* dev, const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K,
                     int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t stream, bool bf16) {
     const uint32_t extra = bf16 ? kIdescBf16Inputs : 0u;
-    int plan = gemm_tile_plan(M, N, K, dev->sm_count);
-    if (const char* force = getenv("TC_GEMM_PAIR_TILE")) {   // "tall" or "square": overrides the pair tile (tuning aid)
-        if (plan == TC_GEMM_TILE_PAIR_256x256 && force[0] == 't') plan = TC_GEMM_TILE_PAIR_512x256;
-        if (plan == TC_GEMM_TILE_PAIR_512x256 && force[0] == 's') plan = TC_GEMM_TILE_PAIR_256x256;
-    }
+    const int plan = gemm_tile_plan(M, N, K, dev->sm_count);
     const bool use_pair = plan == TC_GEMM_TILE_PAIR_256x256 || plan == TC_GEMM_TILE_PAIR_512x256;
     const uint32_t bn = plan == TC_GEMM_TILE_128x256 ? 256u : (plan == TC_GEMM_TILE_128x64 ? 64u : 128u);
     CUtensorMap ta, tb;

@@ -80,15 +80,8 @@ extern "C" int tc_gemm_f16_f32_host(const void* hA, const void* hB, void* hC, in
     auto* dC = dB + N * K * 2;
     TCB_REQUIRE((reinterpret_cast<uintptr_t>(dB) & 15u) == 0 && (reinterpret_cast<uintptr_t>(dC) & 15u) == 0,
                 "gemm_host: M*K and N*K must keep the staging areas 16-byte aligned");
-    int sa = static_cast<int>(M >= 2048 ? (M >= 8192 ? 4 : 2) : 1);
-    int sb = static_cast<int>(N >= 2048 ? (N >= 8192 ? 4 : 2) : 1);
-    if (const char* env = getenv("TC_GEMM_HOST_SLABS")) {  // tuning knob: "row_slabs,col_slabs", each 1..8
-        int ea = 0, eb = 0;
-        if (sscanf(env, "%d,%d", &ea, &eb) == 2 && ea >= 1 && ea <= kHostMaxSlabs && eb >= 1 && eb <= kHostMaxSlabs) {
-            sa = ea;
-            sb = eb;
-        }
-    }
+    const int sa = static_cast<int>(M >= 2048 ? (M >= 8192 ? 4 : 2) : 1);
+    const int sb = static_cast<int>(N >= 2048 ? (N >= 8192 ? 4 : 2) : 1);
     const int64_t ra = slab_rows(M, sa), rb = slab_rows(N, sb);
 
     // uploads follow everything already queued on the caller's stream

@@ -235,10 +235,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 // operand traffic this shape saves against 256x256 tiles.
 constexpr int kTallBK = 64;
 constexpr int kTallStages = 4;
-#ifndef TC_TALL_ROUND
-#define TC_TALL_ROUND 2
-#endif
-constexpr int kTallRound = TC_TALL_ROUND;   // K blocks issued per barrier round (<= kTallStages)
+constexpr int kTallRound = 2;   // K blocks issued per barrier round (<= kTallStages)
 constexpr int kTallABytes = 2 * kPairBM * kTallBK * 2;          // 256 rows
 constexpr int kTallBBytes = (kPairBN / 2) * kTallBK * 2;        // 128 of the 256 B rows
 constexpr int kTallStageBytes = kTallABytes + kTallBBytes;
@@ -442,11 +439,8 @@ int launch_gemm_pair_tall(const CUtensorMap& ta, const CUtensorMap& tb, float* C
     CUtensorMap tc;
     int use_tma = 0;
     if (int rc = output_store_map(&tc, &use_tma, C, M, N, ldc)) return rc;
-    static bool configured[64] = {};
-    if (!configured[dev->device]) {
-        TCB_CUDA(cudaFuncSetAttribute(gemm_pair_tall_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTallSmem));
-        configured[dev->device] = true;
-    }
+    static OncePerDevice once;
+    if (int rc = raise_smem_limit_once(once, dev->device, gemm_pair_tall_kernel, kTallSmem)) return rc;
     const int tiles_m = (M + 4 * kPairBM - 1) / (4 * kPairBM);
     const int tiles_n = (N + kPairBN - 1) / kPairBN;
     const int tiles = tiles_m * tiles_n;
@@ -462,11 +456,8 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, float* C, int
     CUtensorMap tc;
     int use_tma = 0;
     if (int rc = output_store_map(&tc, &use_tma, C, M, N, ldc)) return rc;
-    static bool configured[64] = {};
-    if (!configured[dev->device]) {
-        TCB_CUDA(cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem));
-        configured[dev->device] = true;
-    }
+    static OncePerDevice once;
+    if (int rc = raise_smem_limit_once(once, dev->device, gemm_pair_kernel, kPairSmem)) return rc;
     const int tiles_m = (M + 2 * kPairBM - 1) / (2 * kPairBM);
     const int tiles_n = (N + kPairBN - 1) / kPairBN;
     const int tiles = tiles_m * tiles_n;

@@ -8,6 +8,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/tiledcuda_b200.h"
 
 namespace tcb {
@@ -52,6 +54,24 @@ int encode_tmap_f32_sw128(CUtensorMap* out, const void* base, uint64_t cols, uin
 // The same for a [batch, rows, cols] fp32 array (cols innermost, dense): boxes of box_cols x box_rows x 1.
 int encode_tmap_f32_sw128_3d(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint64_t batch,
                              uint32_t box_cols, uint32_t box_rows);
+
+// One-time, per-device set-up of a kernel (its dynamic shared-memory limit), safe against concurrent first calls
+// from several host threads: every launcher keeps one of these per kernel and calls raise_smem_limit_once() with it.
+struct OncePerDevice {
+    std::mutex mu;
+    bool done[64] = {};
+};
+
+template <typename Kernel>
+inline int raise_smem_limit_once(OncePerDevice& once, int device, Kernel kernel, int bytes) {
+    if (device < 0 || device >= 64) return fail(TC_ERR_UNSUPPORTED, "device ordinal %d out of range", device);
+    std::lock_guard<std::mutex> lock(once.mu);
+    if (!once.done[device]) {
+        TCB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+        once.done[device] = true;
+    }
+    return TC_OK;
+}
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

@@ -352,11 +352,8 @@ static int launch_lstm(const CUtensorMap& tx, const LstmWeights& lw, const CUten
                        const DeviceInfo* dev, cudaStream_t stream) {
     using Cfg = LstmCfg<HT>;
     auto kernel = lstm_cell_kernel<HT>;
-    static bool configured[64] = {};
-    if (!configured[dev->device]) {
-        TCB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
-        configured[dev->device] = true;
-    }
+    static OncePerDevice once;
+    if (int rc = raise_smem_limit_once(once, dev->device, kernel, Cfg::kSmem)) return rc;
     const dim3 grid(static_cast<unsigned>((p.hidden + HT - 1) / HT), static_cast<unsigned>((p.batch + kLstmBM - 1) / kLstmBM));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -553,9 +550,24 @@ extern "C" int tc_lstm_chain_static_f16(const void* W, const void* U, const floa
                                         const float* c0, void* h_all, float* c_out, int64_t steps, int64_t batch,
                                         int64_t input, int64_t hidden, tc_stream_t stream) {
     using namespace tcb;
+    auto* st = static_cast<cudaStream_t>(stream);
+    // Argument checks first (they need no device), so that a bad call is refused before anything is set up.
+    TCB_REQUIRE(steps >= 0, "lstm_chain_static: steps must not be negative");
+    if (steps > 0) {
+        if (int rc = check_lstm("lstm_chain_static", W, U, x, h0, c0, h_all, c_out, batch, input, hidden)) return rc;
+        TCB_REQUIRE((batch * input) % 8 == 0 && (batch * hidden) % 8 == 0,
+                    "lstm_chain_static: per-step slabs must stay 16-byte aligned");
+        // The limit is tested by division, so that an absurd `steps` cannot wrap the product past it; within the
+        // limit steps * batch (the row count of the hoisted GEMM) is far below 2^31.
+        const int64_t bytes_per_step = batch * 4 * hidden * static_cast<int64_t>(sizeof(float));
+        if (steps > kStaticScratchBytes / bytes_per_step)
+            return fail(TC_ERR_UNSUPPORTED,
+                        "lstm_chain_static: %lld steps of %lld bytes of scratch each exceed the %lld bytes built into "
+                        "the library; use tc_lstm_chain_ws_f16 with your own workspace or tc_lstm_chain_f16",
+                        (long long)steps, (long long)bytes_per_step, (long long)kStaticScratchBytes);
+    }
     const StaticDevice* sd = nullptr;
     if (int rc = static_device(&sd)) return rc;
-    auto* st = static_cast<cudaStream_t>(stream);
     if (steps == 0) {
         // Status query for this path: its kernels record timeouts in the library's own status word, which
         // tc_device_status() does not see. Synchronises the device; launches nothing.
@@ -568,16 +580,6 @@ extern "C" int tc_lstm_chain_static_f16(const void* W, const void* U, const floa
         }
         return TC_OK;
     }
-    TCB_REQUIRE(steps > 0, "lstm_chain_static: steps must not be negative");
-    if (int rc = check_lstm("lstm_chain_static", W, U, x, h0, c0, h_all, c_out, batch, input, hidden)) return rc;
-    TCB_REQUIRE((batch * input) % 8 == 0 && (batch * hidden) % 8 == 0,
-                "lstm_chain_static: per-step slabs must stay 16-byte aligned");
-    const int64_t need = steps * batch * 4 * hidden * static_cast<int64_t>(sizeof(float));
-    if (need > kStaticScratchBytes)
-        return fail(TC_ERR_UNSUPPORTED,
-                    "lstm_chain_static: steps * batch * 4 * hidden * 4 = %lld bytes of scratch exceed the %lld bytes built into "
-                    "the library; use tc_lstm_chain_ws_f16 with your own workspace or tc_lstm_chain_f16",
-                    (long long)need, (long long)kStaticScratchBytes);
     const DeviceInfo* dev = &sd->info;
     LstmWeights lw;
     if (int rc = encode_weights(&lw, dev, W, U, batch, input, hidden)) return rc;

@@ -9,6 +9,7 @@
 #include <c10/cuda/CUDAStream.h>
 #include <torch/library.h>
 
+#include <initializer_list>
 #include <vector>
 
 #include "../../include/tiledcuda_b200.h"
@@ -29,17 +30,38 @@ void need(const at::Tensor& t, const char* name, at::ScalarType dtype) {
     TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
 }
 
+// Every tensor of a call lives on the device of the first one: the C ABI takes raw pointers and cannot tell.
+void same_device(const char* op, const at::Tensor& first, std::initializer_list<const at::Tensor*> rest) {
+    for (const at::Tensor* t : rest)
+        TORCH_CHECK(t->device() == first.device(), op, ": all tensors must be on one device (got ", first.device(), " and ",
+                    t->device(), ")");
+}
+
+// Shape rules shared by both scatter ops: indices [..., k] with k <= data.dim(), and updates holding exactly one
+// slice (the trailing data.dim() - k dimensions of data) per index tuple. Returns n, the number of tuples.
+int64_t scatter_shapes(const char* op, const at::Tensor& data, const at::Tensor& updates, const at::Tensor& indices) {
+    TORCH_CHECK(data.is_cuda() && updates.is_cuda() && indices.is_cuda(), op, " needs CUDA tensors");
+    same_device(op, data, {&updates, &indices});
+    TORCH_CHECK(data.is_contiguous() && updates.is_contiguous() && indices.is_contiguous(), op, " needs contiguous tensors");
+    TORCH_CHECK(updates.scalar_type() == data.scalar_type(), op, ": updates and data must have the same dtype");
+    TORCH_CHECK(indices.scalar_type() == at::kLong || indices.scalar_type() == at::kInt, op, ": indices must be int32 or int64");
+    TORCH_CHECK(indices.dim() >= 1 && data.dim() >= 1, op, ": indices and data must have at least one dimension");
+    const int64_t k = indices.size(-1);
+    TORCH_CHECK(k >= 1 && k <= data.dim(), op, ": index tuples of length ", k, " do not fit a table of rank ", data.dim());
+    const int64_t n = indices.numel() / k;
+    int64_t slice = 1;
+    for (int64_t i = k; i < data.dim(); ++i) slice *= data.size(i);
+    TORCH_CHECK(updates.numel() == n * slice, op, ": updates has ", updates.numel(), " elements, ", n, " tuples of ", slice,
+                " elements need ", n * slice);
+    return n;
+}
+
 // Same argument order as the reference's custom_scatter_op(data, updates, indices)
 // (include/kernels/scatter_nd.hpp:39-40). data keeps its N-D shape; indices is [..., k].
 void scatter_nd_op(at::Tensor& data, const at::Tensor& updates, const at::Tensor& indices) {
-    TORCH_CHECK(data.is_cuda() && updates.is_cuda() && indices.is_cuda(), "scatter_nd needs CUDA tensors");
-    TORCH_CHECK(data.is_contiguous() && updates.is_contiguous() && indices.is_contiguous(), "scatter_nd needs contiguous tensors");
-    TORCH_CHECK(updates.scalar_type() == data.scalar_type(), "updates and data must have the same dtype");
+    const int64_t n = scatter_shapes("scatter_nd", data, updates, indices);
     const bool i64 = indices.scalar_type() == at::kLong;
-    TORCH_CHECK(i64 || indices.scalar_type() == at::kInt, "indices must be int32 or int64");
-    TORCH_CHECK(indices.dim() >= 1, "indices must have at least one dimension");
     const int64_t k = indices.size(-1);
-    const int64_t n = k > 0 ? indices.numel() / k : 0;
     std::vector<int64_t> dims(data.sizes().begin(), data.sizes().end());
     c10::cuda::CUDAGuard guard(data.device());
     check("scatter_nd", tc_scatter_nd(data.data_ptr(), updates.data_ptr(), indices.data_ptr(), i64 ? 1 : 0, dims.data(),
@@ -49,9 +71,7 @@ void scatter_nd_op(at::Tensor& data, const at::Tensor& updates, const at::Tensor
 
 // The accumulating form, which is what the reference's kernel does (src/kernels/scatter_nd.cu:44-47).
 void scatter_nd_add_op(at::Tensor& data, const at::Tensor& updates, const at::Tensor& indices) {
-    TORCH_CHECK(data.is_cuda() && updates.is_cuda() && indices.is_cuda(), "scatter_nd_add needs CUDA tensors");
-    TORCH_CHECK(data.is_contiguous() && updates.is_contiguous() && indices.is_contiguous(), "scatter_nd_add needs contiguous tensors");
-    TORCH_CHECK(updates.scalar_type() == data.scalar_type(), "updates and data must have the same dtype");
+    const int64_t n = scatter_shapes("scatter_nd_add", data, updates, indices);
     int elem_type = -1;
     switch (data.scalar_type()) {
         case at::kFloat: elem_type = 0; break;
@@ -61,10 +81,7 @@ void scatter_nd_add_op(at::Tensor& data, const at::Tensor& updates, const at::Te
         default: TORCH_CHECK(false, "scatter_nd_add supports float32, float16, int32 and float64 tables");
     }
     const bool i64 = indices.scalar_type() == at::kLong;
-    TORCH_CHECK(i64 || indices.scalar_type() == at::kInt, "indices must be int32 or int64");
-    TORCH_CHECK(indices.dim() >= 1, "indices must have at least one dimension");
     const int64_t k = indices.size(-1);
-    const int64_t n = k > 0 ? indices.numel() / k : 0;
     std::vector<int64_t> dims(data.sizes().begin(), data.sizes().end());
     c10::cuda::CUDAGuard guard(data.device());
     check("scatter_nd_add", tc_scatter_nd_add(data.data_ptr(), updates.data_ptr(), indices.data_ptr(), i64 ? 1 : 0, dims.data(),
@@ -79,6 +96,8 @@ void flash_attention_fwd_op(const at::Tensor& Q, const at::Tensor& K, const at::
     need(K, "K", at::kHalf);
     need(V, "V", at::kHalf);
     need(O, "O", at::kHalf);
+    same_device("flash_attention_fwd", Q, {&K, &V, &O});
+    TORCH_CHECK(m > 0 && n > 0 && k > 0 && p > 0, "flash_attention_fwd: m, n, k, p must be positive");
     TORCH_CHECK(Q.numel() == m * k && K.numel() == n * k && V.numel() == n * p && O.numel() == m * p,
                 "flash_attention_fwd: tensor sizes do not match m, n, k, p");
     c10::cuda::CUDAGuard guard(Q.device());
@@ -93,6 +112,7 @@ void flash_attn_op(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& V
     need(K, "K", at::kHalf);
     need(V, "V", at::kHalf);
     need(O, "O", at::kHalf);
+    same_device("flash_attn", Q, {&K, &V, &O});
     TORCH_CHECK(Q.dim() == 4 && K.dim() == 4 && V.dim() == 4 && O.dim() == 4, "flash_attn: tensors must be [B,H,S,D]");
     const int64_t b = Q.size(0), h = Q.size(1), sq = Q.size(2), d = Q.size(3), skv = K.size(2);
     const int64_t dv = v_is_transposed ? V.size(2) : V.size(3);
@@ -111,11 +131,13 @@ void flash_attn_ex_op(const at::Tensor& Q, const at::Tensor& K, const at::Tensor
     need(K, "K", at::kHalf);
     need(V, "V", at::kHalf);
     need(O, "O", at::kHalf);
+    same_device("flash_attn_ex", Q, {&K, &V, &O});
     TORCH_CHECK(Q.dim() == 4 && K.dim() == 4 && V.dim() == 4 && O.dim() == 4, "flash_attn_ex: tensors must be 4-D");
     const int sd = seq_major ? 1 : 2, hd = seq_major ? 2 : 1;
     const int64_t b = Q.size(0), h = Q.size(hd), sq = Q.size(sd), d = Q.size(3), skv = K.size(sd), dv = V.size(3);
     TORCH_CHECK(K.size(0) == b && K.size(hd) == h && K.size(3) == d, "flash_attn_ex: K shape mismatch");
     TORCH_CHECK(V.size(0) == b && V.size(hd) == h && V.size(sd) == skv, "flash_attn_ex: V shape mismatch");
+    TORCH_CHECK(K.size(sd) == skv, "flash_attn_ex: K shape mismatch");
     TORCH_CHECK(O.size(0) == b && O.size(hd) == h && O.size(sd) == sq && O.size(3) == dv, "flash_attn_ex: O shape mismatch");
     c10::cuda::CUDAGuard guard(Q.device());
     check("flash_attn_ex", tc_flash_attn_fwd_ex_f16(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), nullptr, b, h, sq, skv, d,
@@ -127,6 +149,7 @@ void gemm_op(const at::Tensor& A, const at::Tensor& B, at::Tensor& C) {
     need(A, "A", at::kHalf);
     need(B, "B", at::kHalf);
     need(C, "C", at::kFloat);
+    same_device("gemm", A, {&B, &C});
     TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && C.dim() == 2, "gemm: tensors must be 2-D");
     TORCH_CHECK(B.size(1) == A.size(1) && C.size(0) == A.size(0) && C.size(1) == B.size(0), "gemm: shape mismatch");
     c10::cuda::CUDAGuard guard(A.device());
@@ -140,11 +163,13 @@ void back2back_gemm_op(const at::Tensor& A, const at::Tensor& B, const at::Tenso
     need(B, "B", at::kHalf);
     need(D, "D", at::kHalf);
     need(E, "E", at::kFloat);
+    same_device("back2back_gemm", A, {&B, &D, &E});
     TORCH_CHECK((A.dim() == 2 || A.dim() == 3) && B.dim() == A.dim() && D.dim() == A.dim() && E.dim() == A.dim(),
                 "back2back_gemm: tensors must all be 2-D or all 3-D");
     const int64_t batch = A.dim() == 3 ? A.size(0) : 1;
     const int64_t m = A.size(-2), k = A.size(-1), n = B.size(-2), p = D.size(-2);
     TORCH_CHECK(B.size(-1) == k && D.size(-1) == n && E.size(-2) == m && E.size(-1) == p, "back2back_gemm: shape mismatch");
+    TORCH_CHECK(A.dim() == 2 || (B.size(0) == batch && D.size(0) == batch && E.size(0) == batch), "back2back_gemm: batch mismatch");
     c10::cuda::CUDAGuard guard(A.device());
     check("back2back_gemm", tc_b2b_gemm_f16(A.data_ptr(), B.data_ptr(), D.data_ptr(), E.data_ptr(), m, n, k, p, batch, stream_of(A)));
 }
@@ -164,8 +189,18 @@ void lstm_cell_op(const at::Tensor& W, const at::Tensor& U, const c10::optional<
         need(*bias, "bias", at::kFloat);
         b = bias->data_ptr<float>();
     }
+    same_device("lstm_cell", x, {&W, &U, &h_prev, &c_prev, &h_out, &c_out});
+    TORCH_CHECK(W.dim() == 2 && U.dim() == 2 && x.dim() == 2, "lstm_cell: W, U and x must be 2-D");
     const int64_t batch = x.size(0), input = x.size(1), hidden = U.size(1);
     TORCH_CHECK(W.size(0) == 4 * hidden && W.size(1) == input && U.size(0) == 4 * hidden, "lstm_cell: weight shape mismatch");
+    for (const at::Tensor* t : std::initializer_list<const at::Tensor*>{&h_prev, &c_prev, &h_out, &c_out})
+        TORCH_CHECK(t->dim() == 2 && t->size(0) == batch && t->size(1) == hidden, "lstm_cell: h_prev, c_prev, h_out and c_out must be [",
+                    batch, ", ", hidden, "], got ", t->sizes());
+    if (b != nullptr) {
+        same_device("lstm_cell", x, {&*bias});
+        TORCH_CHECK(bias->numel() == 4 * hidden, "lstm_cell: bias must have 4 * hidden = ", 4 * hidden, " elements, got ", bias->numel());
+    }
+    TORCH_CHECK(h_out.data_ptr() != h_prev.data_ptr(), "lstm_cell: h_out must not alias h_prev");
     c10::cuda::CUDAGuard guard(x.device());
     check("lstm_cell", tc_lstm_cell_f16(W.data_ptr(), U.data_ptr(), b, x.data_ptr(), h_prev.data_ptr(), c_prev.data_ptr<float>(),
                                         h_out.data_ptr(), c_out.data_ptr<float>(), batch, input, hidden, stream_of(x)));

@@ -18,18 +18,15 @@
 
 namespace tiledcuda::cell::copy {
 
-// 64-bit shared-memory matrix descriptor of a 16-bit operand tile for tcgen05.mma; `k` selects the
-// 16-element K step inside the tile.
+// 64-bit shared-memory matrix descriptor of a 16-bit operand tile (a SharedTile, or a chunk of one from an
+// STileIterator) for tcgen05.mma; `k_step` selects the 16-element K step inside it.
 template <typename Shared>
 DEVICE uint64_t make_operand_descriptor(const Shared& tile, int k_step = 0) {
     static_assert(Shared::kIsOperand, "only 16-bit shared tiles are MMA operands");
     using Op = typename Shared::Operand;
-    uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(tile.data()));
-    if constexpr (Op::kSwizzled) {
-        addr += static_cast<uint32_t>((k_step >> 2) * Op::kChunkBytes + (k_step & 3) * 32);
-    } else {
-        addr += static_cast<uint32_t>(k_step * 2 * Op::kLbo);  // 16 elements = two 8x8 core matrices along K
-    }
+    // a whole SharedTile starts at data(); a chunk handed out by an STileIterator starts inside its parent
+    const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(tile.data())) +
+                          static_cast<uint32_t>(tile.operand_offset_bytes(k_step));
     uint64_t d = 0;
     d |= static_cast<uint64_t>((addr & 0x3ffffu) >> 4);
     d |= static_cast<uint64_t>((Op::kLbo >> 4) & 0x3fff) << 16;

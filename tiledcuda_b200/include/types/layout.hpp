@@ -7,12 +7,13 @@
 //       K chunks of 8-row, 1024-byte atoms whose 16-byte pieces are XOR-permuted by the row; without, the
 //       interleaved layout of 8x8 core matrices. They take the place of the reference's BaseTile-blocked
 //       Swizzle<2,3,3> layouts (layout.hpp:58-206), which were shaped for ldmatrix;
-//   SharedLayoutWrapper<Shared>                                             picks one of the two from a
-//       SharedTile's flags, as layout.hpp:208-273 does.
+//   SharedLayoutWrapper<Shared>::Layout                                     the storage layout of a shared tile
+//       picked from its element width and kSwizzled flag, as layout.hpp:208-273 does.
 // All of it is constexpr arithmetic and compiles on the host.
 #pragma once
 
 #include <cstddef>
+#include <type_traits>
 
 #include "cell/traits/base.hpp"
 #include "config.hpp"
@@ -91,6 +92,15 @@ struct OperandLayout {
         }
     }
     HOST_DEVICE constexpr int operator()(int o, int k) const { return byte_offset(o, k) / kElemBytes; }
+};
+
+// Storage layout of a shared tile: the operand layout (swizzled or interleaved, by the tile's kSwizzled flag)
+// for a 16-bit tile, the tile's own strided layout for a 32-bit one. For a column-major operand tile the
+// operand layout is indexed (col, row): its first index is the outer (N) extent.
+template <typename Shared>
+struct SharedLayoutWrapper {
+    static constexpr bool kIsOperand = Shared::kIsOperand;
+    using Layout = std::conditional_t<kIsOperand, OperandLayout<Shared::kOuter, Shared::kK, Shared::kSwizzled>, typename Shared::Layout>;
 };
 
 }  // namespace tile_layout

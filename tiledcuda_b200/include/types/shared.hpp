@@ -53,6 +53,17 @@ class SharedTile {
     HOST_DEVICE DType& operator()(int x, int y) { return data_[offset(x, y)]; }
     HOST_DEVICE const DType& operator()(int x, int y) const { return data_[offset(x, y)]; }
 
+    // Byte distance from data() to where the MMA descriptor of K step `k_step` (16 elements) starts: inside a
+    // 128-byte swizzle row a step is 32 bytes, every fourth step moves to the next 64-element chunk; in the
+    // interleaved layout a step is two 8x8 core matrices along K.
+    HOST_DEVICE static constexpr int operand_offset_bytes(int k_step) {
+        if constexpr (Operand::kSwizzled) {
+            return (k_step >> 2) * Operand::kChunkBytes + (k_step & 3) * 32;
+        } else {
+            return k_step * 2 * Operand::kLbo;
+        }
+    }
+
   private:
     DType* data_;
 };
