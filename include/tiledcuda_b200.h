@@ -47,6 +47,14 @@ int tc_device_status(int* code);
 int tc_gemm_f16_f32(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
                     int64_t ldb, int64_t ldc, tc_stream_t stream);
 
+/* tc_gemm_f16_f32 on at most max_sms streaming multiprocessors (0 = all of them): the tile plan and the persistent
+ * grid are sized for that budget and the other SMs stay free for kernels that run beside the GEMM, e.g. the
+ * collective that assembles finished row blocks of C on the other GPUs while later blocks are computed. The
+ * reference is single-GPU and sizes its grid by the problem alone (examples/cpp/01_gemm/02_gemm_all_mem/main.cu:67-71);
+ * it has no counterpart there. */
+int tc_gemm_f16_f32_sms(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                        int64_t ldb, int64_t ldc, int max_sms, tc_stream_t stream);
+
 /* The same GEMM with bf16 A and B (fp32 accumulate and output). The reference is fp16-only
  * (include/cell/compute/gemm.hpp:26-29 static_asserts); it has no counterpart there. */
 int tc_gemm_bf16_f32(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,

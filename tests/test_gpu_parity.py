@@ -33,6 +33,7 @@ GEMM_SHAPES = [
         (300, 520, 4096), (1536, 1536, 1536),    # few pair tiles with a long K loop
         (1290, 1410, 136),                       # lone 128x128 tiles with ragged edges
         (4000, 4090, 520),                       # 256 pair tiles on 74 pairs: three full waves and a partial one
+        (640, 384, 576), (1000, 900, 1096), (130, 70, 520), (1024, 1024, 256),  # single partial wave: odd K-block counts, ragged edges
     ]
 
 
@@ -64,6 +65,21 @@ def test_gemm_leading_dimensions_and_guard_bands(cuda_ops, clean_status):
     assert_close(c, oracle.gemm(a_full[:, :k], b_full[:, :k]), max_abs=2e-3, rel_fro=1e-5)
     guard = c_store.clone()
     guard[1:m + 1, 4:n + 4] = -7.0
+    assert (guard == -7.0).all(), "GEMM wrote outside its output"
+
+
+@pytest.mark.parametrize("col_off,extra", [(4, 8), (1, 7)])
+def test_gemm_guard_bands_aligned_and_unaligned_output(cuda_ops, clean_status, col_off, extra):
+    """A single partial wave of tiles writing into a window of a larger buffer: with a 16-byte granular window the
+    kernel stores through TMA, otherwise from registers; neither may touch the guard band around the window."""
+    m, n, k = 900, 650, 1024
+    a, b = oracle.gemm_inputs(m, n, k)
+    c_store = torch.full((m + 2, n + extra), -7.0, device=DEV)
+    c = c_store[1:m + 1, col_off:n + col_off]
+    cuda_ops.gemm(a.to(DEV), b.to(DEV), c)
+    assert_close(c, oracle.gemm(a, b), max_abs=2e-3, rel_fro=1e-5)
+    guard = c_store.clone()
+    guard[1:m + 1, col_off:n + col_off] = -7.0
     assert (guard == -7.0).all(), "GEMM wrote outside its output"
 
 
@@ -125,12 +141,15 @@ def test_gemm_headline_sizes_on_the_benchmark_inputs(cuda_ops, clean_status, n):
     rows = torch.tensor(rows)
     assert rows.numel() == 96
     got = c[rows.to(DEV)].cpu()
-    assert_close(got, oracle.gemm(a[rows], b), max_abs=2e-3, rel_fro=1e-5)
+    # The tensor core adds each K = 16 partial product into its fp32 accumulator with truncation, so the error grows
+    # with the number of accumulation steps (K / 16): about 2e-3 at K = 8192 on entries of magnitude 30-150, twice that
+    # at 16384. Bounds: half the stated max-abs tolerance of the path (2e-2) and a twentieth of its relative one (1e-3).
+    assert_close(got, oracle.gemm(a[rows], b), max_abs=1e-2, rel_fro=5e-5)
     # checksum over every row: sum_i C[i, :] against (sum_i A[i, :]) B^T in float64
     col_sums = c.double().sum(dim=0).cpu()
     want = (a.double().sum(dim=0, keepdim=True) @ b.double().t()).view(-1)
     assert not torch.isnan(col_sums).any()
-    assert (col_sums - want).abs().max().item() <= 2e-3 * math.sqrt(n) * 4
+    assert (col_sums - want).abs().max().item() <= 2e-2 * math.sqrt(n)   # n entries whose errors have random signs
 
 
 @pytest.mark.gpu

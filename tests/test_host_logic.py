@@ -94,6 +94,19 @@ def _gloo_worker(rank, world, port, ragged, q):
         full[r0:r1] = slab
         shard.all_gather_slabs(full, world, rank)
         want = torch.from_numpy(oracle.scatter_nd(table.numpy(), idx.numpy(), upd.numpy()))
+
+        # block-wise assembly (what the overlapped GEMM does per finished row block): each rank fills its own
+        # slab, then the slabs are exchanged two row blocks at a time with grouped send / receive
+        if not ragged:
+            ranges = [shard.aligned_shard_range(m, world, r, 128) for r in range(world)]
+            c2 = torch.zeros(m, 48)
+            s2, e2 = ranges[rank]
+            c2[s2:e2] = oracle.gemm(a[s2:e2], b)
+            half = (e2 - s2) // 2
+            for lo, hi in ((0, half), (half, e2 - s2)):
+                for w in shard.exchange_row_block(c2, ranges, lo, hi):
+                    w.wait()
+            ok_gather = ok_gather and torch.equal(c2, oracle.gemm(a, b))
         q.put((rank, start, stop, bool(ok_gather), bool(torch.equal(full, want))))
     finally:
         dist.destroy_process_group()
@@ -126,3 +139,8 @@ def test_torch_op_library_registers_the_reference_ops_and_has_no_cpu_kernel():
         pytiledcuda.gemm(a, a, torch.zeros(8, 8))
     for name in ("scatter_nd", "flash_attention_fwd", "TiledFlashAttention"):
         assert hasattr(pytiledcuda, name)
+    # and under the reference's own package name
+    import pytiledcuda as by_reference_name
+
+    assert by_reference_name.TiledFlashAttention is pytiledcuda.TiledFlashAttention
+    assert by_reference_name.scatter_nd is pytiledcuda.scatter_nd

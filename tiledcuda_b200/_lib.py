@@ -22,6 +22,7 @@ SIGNATURES = {
     "tc_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
     "tc_gemm_f16_f32": (ctypes.c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp]),
     "tc_gemm_bf16_f32": (ctypes.c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp]),
+    "tc_gemm_f16_f32_sms": (ctypes.c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, ctypes.c_int, c_vp]),
     "tc_gemm_tile_plan": (ctypes.c_int, [c_i64, c_i64, c_i64, ctypes.c_int]),
     "tc_gemm_host_workspace_bytes": (c_i64, [c_i64, c_i64, c_i64]),
     "tc_gemm_f16_f32_host": (ctypes.c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_i64, c_vp]),

@@ -277,8 +277,13 @@ int gemm_tile_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
 // The dispatch of tc_gemm_f16_f32 for a caller that brings its own device record (and therefore its own
 // status word) instead of the lazily allocated per-device one. Arguments are trusted: the caller has
 // validated them. Used by entry points that must not allocate.
-int gemm_f16_f32_on(const DeviceInfo* dev, const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K,
-                    int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t stream, bool bf16) {
+int gemm_f16_f32_on(const DeviceInfo* dev_full, const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K,
+                    int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t stream, bool bf16, int sm_limit) {
+    // With an SM budget the tile plan and the persistent grids are sized for that many SMs, the rest stay free
+    // for whatever else the caller runs beside the GEMM (a collective that assembles finished blocks, say).
+    DeviceInfo limited = *dev_full;
+    if (sm_limit > 0 && sm_limit < limited.sm_count) limited.sm_count = sm_limit;
+    const DeviceInfo* dev = &limited;
     const uint32_t extra = bf16 ? kIdescBf16Inputs : 0u;
     const int plan = gemm_tile_plan(M, N, K, dev->sm_count);
     const bool use_pair = plan == TC_GEMM_TILE_PAIR_256x256 || plan == TC_GEMM_TILE_PAIR_512x256;
@@ -306,7 +311,7 @@ int gemm_f16_f32_on(const DeviceInfo* dev, const void* A, const void* B, float* 
 }  // namespace tcb
 
 static int gemm_entry(const char* op, bool bf16, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
-                      int64_t lda, int64_t ldb, int64_t ldc, tc_stream_t stream) {
+                      int64_t lda, int64_t ldb, int64_t ldc, tc_stream_t stream, int sm_limit = 0) {
     using namespace tcb;
     TCB_REQUIRE(A && B && C, "%s: null pointer argument", op);
     TCB_REQUIRE(M > 0 && N > 0 && K > 0, "%s: M, N, K must be positive (got %lld, %lld, %lld)", op, (long long)M,
@@ -321,12 +326,21 @@ static int gemm_entry(const char* op, bool bf16, const void* A, const void* B, v
     if (int rc = current_device(&dev)) return rc;
     // Large problems run 256x256 tiles on CTA pairs; narrow or small ones take lone CTAs with 128x256 or
     // 128x128 tiles so that more SMs are busy (the choice is made in gemm_f16_f32_on).
-    return gemm_f16_f32_on(dev, A, B, static_cast<float*>(C), M, N, K, lda, ldb, ldc, static_cast<cudaStream_t>(stream), bf16);
+    return gemm_f16_f32_on(dev, A, B, static_cast<float*>(C), M, N, K, lda, ldb, ldc, static_cast<cudaStream_t>(stream), bf16,
+                           sm_limit);
 }
 
 extern "C" int tc_gemm_f16_f32(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
                                int64_t ldb, int64_t ldc, tc_stream_t stream) {
     return gemm_entry("gemm", false, A, B, C, M, N, K, lda, ldb, ldc, stream);
+}
+
+extern "C" int tc_gemm_f16_f32_sms(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                                   int64_t ldb, int64_t ldc, int max_sms, tc_stream_t stream) {
+    using namespace tcb;
+    TCB_REQUIRE(max_sms >= 0, "gemm_sms: max_sms must not be negative (0 = all SMs)");
+    TCB_REQUIRE(max_sms == 0 || max_sms >= 2, "gemm_sms: a budget needs at least 2 SMs (one CTA pair)");
+    return gemm_entry("gemm_sms", false, A, B, C, M, N, K, lda, ldb, ldc, stream, max_sms);
 }
 
 extern "C" int tc_gemm_bf16_f32(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,

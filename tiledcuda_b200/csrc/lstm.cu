@@ -20,7 +20,7 @@ namespace tcb {
 
 // GEMM dispatch for a caller-supplied device record (gemm.cu).
 int gemm_f16_f32_on(const DeviceInfo* dev, const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K,
-                    int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t stream, bool bf16);
+                    int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t stream, bool bf16, int sm_limit = 0);
 
 constexpr int kLstmBM = 128;
 constexpr int kLstmBK = 64;

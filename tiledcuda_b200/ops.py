@@ -50,12 +50,13 @@ def _need(t: torch.Tensor, name: str, dtype: torch.dtype, contiguous: bool = Tru
         raise ValueError(f"{name} must be contiguous")
 
 
-def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> None:
+def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, max_sms: int = 0) -> None:
     """c[M,N] (fp32) = a[M,K] @ b[N,K].T with fp16 (or bf16) inputs and fp32 accumulation.
 
     `b` is the column-major [K,N] operand of the reference's GEMM stored as [N,K] rows, so the result
     equals `a @ b.t()` (examples/python/gemm/main.py:21). Row strides of a, b, c may exceed the row
-    length (leading dimensions); the innermost stride must be 1.
+    length (leading dimensions); the innermost stride must be 1. max_sms > 0 (fp16 only) runs the GEMM on
+    at most that many SMs and leaves the rest to kernels running beside it (tc_gemm_f16_f32_sms).
     """
     in_dtype = torch.bfloat16 if isinstance(a, torch.Tensor) and a.dtype == torch.bfloat16 else torch.float16
     for t, name, dt in ((a, "a", in_dtype), (b, "b", in_dtype), (c, "c", torch.float32)):
@@ -67,6 +68,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> None:
     if kb != k or tuple(c.shape) != (m, n):
         raise ValueError(f"shape mismatch: a {tuple(a.shape)}, b {tuple(b.shape)}, c {tuple(c.shape)}")
     lib = _lib.load()
+    if max_sms:
+        if in_dtype != torch.float16:
+            raise ValueError("max_sms is supported for fp16 inputs only")
+        with _on(a.device):
+            _lib.check("tc_gemm_f16_f32_sms",
+                       lib.tc_gemm_f16_f32_sms(_ptr(a), _ptr(b), _ptr(c), m, n, k, a.stride(0), b.stride(0), c.stride(0),
+                                               int(max_sms), _stream()))
+        return
     fn_name = "tc_gemm_bf16_f32" if in_dtype == torch.bfloat16 else "tc_gemm_f16_f32"
     with _on(a.device):
         _lib.check(

@@ -135,3 +135,134 @@ def sharded_scatter_nd(table_slab: torch.Tensor, row_start: int, indices: torch.
     if local_idx.numel():
         ops.scatter_nd(table_slab, local_idx, local_upd)
     return int(local_idx.shape[0])
+
+
+# ----------------------------------------------------------------------------------------------------
+# Assembling C while it is still being computed
+# ----------------------------------------------------------------------------------------------------
+def exchange_row_block(full: torch.Tensor, ranges, lo: int, hi: int, group=None):
+    """Every rank sends rows [start + lo, start + hi) of its own slab of `full` to every other rank and receives
+    theirs into place (start = first row of the owner's slab): one grouped send/receive over NVLink, zero-copy on
+    both sides because whole rows of `full` are contiguous. Returns the work handles; wait on them (or on the
+    stream they were issued from) before reading the received rows. Slabs must be at least `hi` rows long."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    ops_list = []
+    mine = full[ranges[rank][0] + lo: ranges[rank][0] + hi]
+    for step in range(1, world):
+        # send to rank + step while receiving from rank - step: every link is busy in every slot of the schedule
+        to, frm = (rank + step) % world, (rank - step) % world
+        ops_list.append(dist.P2POp(dist.isend, mine, to, group=group))
+        ops_list.append(dist.P2POp(dist.irecv, full[ranges[frm][0] + lo: ranges[frm][0] + hi], frm, group=group))
+    return dist.batch_isend_irecv(ops_list) if ops_list else []
+
+
+class OverlappedGemm:
+    """c = a @ b.T with the rows of a (and c) split across ranks and C assembled on every rank WHILE it is computed:
+    a rank's slab is cut into row blocks, each block's GEMM runs on the caller's stream on `max_sms` SMs, and as soon
+    as a block is finished it is exchanged with the other ranks from a side stream, so that the transfer of block j
+    runs beside the GEMM of block j + 1 on the SMs the GEMM leaves free. Without a process group this is a plain
+    GEMM. Slabs must be equal and divisible into `blocks` blocks of whole 128-row tiles; otherwise the gather
+    follows the compute (all_gather_slabs)."""
+
+    def __init__(self, blocks: int = 4, max_sms: int = 0):
+        self.blocks = blocks
+        self.max_sms = max_sms
+        self.side = None
+
+    def __call__(self, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, gather: bool = True, group=None) -> Tuple[int, int]:
+        from . import ops
+
+        if not (dist.is_available() and dist.is_initialized()):
+            ops.gemm(a, b, c)
+            return 0, a.shape[0]
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        m = a.shape[0]
+        ranges = [aligned_shard_range(m, world, r, 128) for r in range(world)]
+        start, stop = ranges[rank]
+        rows = stop - start
+        equal = len({hi - lo for lo, hi in ranges}) == 1
+        if not gather or world == 1 or not equal or rows % (self.blocks * 128) != 0:
+            if rows > 0:
+                ops.gemm(a[start:stop], b, c[start:stop])
+            if gather:
+                all_gather_slabs(c, world, rank, ranges, group)
+            return start, stop
+        if self.side is None:
+            self.side = torch.cuda.Stream(device=c.device)
+        main = torch.cuda.current_stream(c.device)
+        per = rows // self.blocks
+        works = []
+        for j in range(self.blocks):
+            lo, hi = j * per, (j + 1) * per
+            # the last block has nothing to hide behind: give it every SM
+            ops.gemm(a[start + lo:start + hi], b, c[start + lo:start + hi], max_sms=self.max_sms if j + 1 < self.blocks else 0)
+            done = torch.cuda.Event()
+            done.record(main)
+            self.side.wait_event(done)
+            with torch.cuda.stream(self.side):
+                works += exchange_row_block(c, ranges, lo, hi, group)
+        for w in works:
+            w.wait()            # the caller's stream waits for the transfers
+        main.wait_stream(self.side)
+        return start, stop
+
+
+class HostGemmPipeline:
+    """The sharded GEMM for callers whose operands live in HOST memory, one rank per GPU:
+
+        this rank's rows of A   host -> device in row blocks (its own slab only),
+        B                       each rank uploads 1/world of it and the ranks all-gather the slices over NVLink,
+                                so that B crosses each host link once in total instead of once per rank,
+        C                       this rank's slab, device -> host block by block as the products finish.
+
+    Uploads, products and downloads run on three streams and overlap. Buffers are allocated once (device staging
+    for the A slab, B and the C slab); host tensors should be pinned. Without a process group the one rank uploads
+    all of B."""
+
+    def __init__(self, rows: int, n: int, k: int, device, blocks: int = 4, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if n % self.world != 0 or rows % blocks != 0:
+            raise ValueError("N must divide by the world size and the slab by the block count")
+        self.rows, self.n, self.k, self.blocks = rows, n, k, blocks
+        self.d_a = torch.empty(rows, k, dtype=torch.float16, device=device)
+        self.d_b = torch.empty(n, k, dtype=torch.float16, device=device)
+        self.d_c = torch.empty(rows, n, dtype=torch.float32, device=device)
+        self.s_in = torch.cuda.Stream(device=device)
+        self.s_out = torch.cuda.Stream(device=device)
+
+    def b_slice(self) -> Tuple[int, int]:
+        per = self.n // self.world
+        return self.rank * per, (self.rank + 1) * per
+
+    def __call__(self, h_a_slab: torch.Tensor, h_b_slice: torch.Tensor, h_c_slab: torch.Tensor) -> None:
+        from . import ops
+
+        main = torch.cuda.current_stream(self.d_a.device)
+        lo, hi = self.b_slice()
+        self.s_in.wait_stream(main)
+        self.s_out.wait_stream(main)
+        with torch.cuda.stream(self.s_in):
+            self.d_b[lo:hi].copy_(h_b_slice, non_blocking=True)
+            b_up = torch.cuda.Event()
+            b_up.record(self.s_in)
+            per = self.rows // self.blocks
+            a_up = []
+            for i in range(self.blocks):
+                self.d_a[i * per:(i + 1) * per].copy_(h_a_slab[i * per:(i + 1) * per], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self.s_in)
+                a_up.append(ev)
+        main.wait_event(b_up)
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.d_b, self.d_b[lo:hi], group=self.group)
+        for i in range(self.blocks):
+            main.wait_event(a_up[i])
+            ops.gemm(self.d_a[i * per:(i + 1) * per], self.d_b, self.d_c[i * per:(i + 1) * per])
+            done = torch.cuda.Event()
+            done.record(main)
+            self.s_out.wait_event(done)
+            with torch.cuda.stream(self.s_out):
+                h_c_slab[i * per:(i + 1) * per].copy_(self.d_c[i * per:(i + 1) * per], non_blocking=True)
+        main.wait_stream(self.s_out)
