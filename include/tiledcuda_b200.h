@@ -186,6 +186,21 @@ int tc_scatter_nd(void* data, const void* updates, const void* indices, int idx_
 int tc_scatter_nd_add(void* data, const void* updates, const void* indices, int idx_is_int64, const int64_t* dims,
                       int rank, int64_t n, int k, int elem_type, tc_stream_t stream);
 
+/* Peer windows, for assembling sharded outputs inside one box with one process per GPU: a rank exports a device
+ * buffer, the other ranks open it and copy their finished blocks straight into it over NVLink on the copy engines
+ * (no SM is taken from the kernels that run beside the copy). tc_peer_export writes an opaque handle of
+ * TC_PEER_HANDLE_BYTES bytes that names the whole device allocation dev_ptr lies in; the handle travels to the other
+ * processes by any host channel. tc_peer_open, called with the opener's own compute device current, returns the base
+ * address of that allocation as seen from the opener (add the exported pointer's offset inside its allocation);
+ * an allocation can be opened once per process. tc_peer_copy queues a device-to-device copy on `stream`; ordering
+ * against the owner's own kernels is the caller's business (a collective or an event shared by the ranks).
+ * tc_peer_close unmaps a window. The reference is single-GPU and single-process; these have no counterpart there. */
+#define TC_PEER_HANDLE_BYTES 64
+int tc_peer_export(const void* dev_ptr, void* handle_out, int64_t handle_bytes);
+int tc_peer_open(const void* handle, int64_t handle_bytes, void** base_out);
+int tc_peer_close(void* base);
+int tc_peer_copy(void* dst, const void* src, int64_t bytes, tc_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -42,6 +42,16 @@ def _worker(rank, world, port, q):
         shard.OverlappedGemm(blocks=4, max_sms=132)(a_d, b_d, c2)
         torch.cuda.synchronize()
         ok["gemm_overlapped"] = bool(torch.equal(c2, c))
+        c3 = torch.full((2048, 640), float("nan"), device=dev)
+        push = shard.OverlappedGemm(blocks=4, transport="copy_engine")
+        push(a_d, b_d, c3)
+        torch.cuda.synchronize()
+        ok["gemm_overlapped_copy_engine"] = bool(torch.equal(c3, c))
+        c3.fill_(float("nan"))
+        dist.barrier()                       # nobody pushes into a C that is still being poisoned
+        push(a_d, b_d, c3)                   # second call: the windows are reused
+        torch.cuda.synchronize()
+        ok["gemm_overlapped_copy_engine_again"] = bool(torch.equal(c3, c))
 
         # the host-operand pipeline: own A slab and half of B from the host, B gathered over NVLink
         pipe = shard.HostGemmPipeline(1024, 640, 512, dev, blocks=4)

@@ -33,7 +33,7 @@ GEMM_SHAPES = [
         (300, 520, 4096), (1536, 1536, 1536),    # few pair tiles with a long K loop
         (1290, 1410, 136),                       # lone 128x128 tiles with ragged edges
         (4000, 4090, 520),                       # 256 pair tiles on 74 pairs: three full waves and a partial one
-        (640, 384, 576), (1000, 900, 1096), (130, 70, 520), (1024, 1024, 256),  # single partial wave: odd K-block counts, ragged edges
+        (640, 384, 576), (1000, 900, 1096), (130, 70, 520), (1024, 1024, 256), (128, 1024, 1024),  # single partial wave: odd K-block counts, ragged edges
     ]
 
 

@@ -50,6 +50,10 @@ SIGNATURES = {
         ctypes.c_int,
         [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_vp],
     ),
+    "tc_peer_export": (ctypes.c_int, [c_vp, c_vp, c_i64]),
+    "tc_peer_open": (ctypes.c_int, [c_vp, c_i64, ctypes.POINTER(c_vp)]),
+    "tc_peer_close": (ctypes.c_int, [c_vp]),
+    "tc_peer_copy": (ctypes.c_int, [c_vp, c_vp, c_i64, c_vp]),
     "tc_scatter_nd": (
         ctypes.c_int,
         [c_vp, c_vp, c_vp, ctypes.c_int, ctypes.POINTER(c_i64), ctypes.c_int, c_i64, ctypes.c_int, ctypes.c_int, c_vp],

@@ -143,4 +143,48 @@ int tc_device_status(int* code) {
     return TC_OK;
 }
 
+// ---- peer windows: another rank's device buffer, addressable from this process -------------------------------
+// One process per GPU. A rank exports a device allocation (cudaIpcGetMemHandle wants a pointer into a cudaMalloc
+// allocation and names the whole allocation), the others open it with the device they compute on current, which
+// maps it into THEIR context with peer access to the owner's GPU. A copy from local memory into such a window is a
+// device-to-device cudaMemcpyAsync over NVLink, executed by the copy engines.
+int tc_peer_export(const void* dev_ptr, void* handle_out, int64_t handle_bytes) {
+    using namespace tcb;
+    TCB_REQUIRE(dev_ptr != nullptr && handle_out != nullptr, "peer_export: null pointer argument");
+    TCB_REQUIRE(handle_bytes >= static_cast<int64_t>(sizeof(cudaIpcMemHandle_t)), "peer_export: the handle buffer holds %lld bytes, %zu needed",
+                (long long)handle_bytes, sizeof(cudaIpcMemHandle_t));
+    cudaIpcMemHandle_t h;
+    TCB_CUDA(cudaIpcGetMemHandle(&h, const_cast<void*>(dev_ptr)));
+    memcpy(handle_out, &h, sizeof(h));
+    return TC_OK;
+}
+
+int tc_peer_open(const void* handle, int64_t handle_bytes, void** base_out) {
+    using namespace tcb;
+    TCB_REQUIRE(handle != nullptr && base_out != nullptr, "peer_open: null pointer argument");
+    TCB_REQUIRE(handle_bytes >= static_cast<int64_t>(sizeof(cudaIpcMemHandle_t)), "peer_open: the handle buffer holds %lld bytes, %zu needed",
+                (long long)handle_bytes, sizeof(cudaIpcMemHandle_t));
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* p = nullptr;
+    TCB_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *base_out = p;
+    return TC_OK;
+}
+
+int tc_peer_close(void* base) {
+    using namespace tcb;
+    if (base == nullptr) return TC_OK;
+    TCB_CUDA(cudaIpcCloseMemHandle(base));
+    return TC_OK;
+}
+
+int tc_peer_copy(void* dst, const void* src, int64_t bytes, tc_stream_t stream) {
+    using namespace tcb;
+    TCB_REQUIRE(dst != nullptr && src != nullptr && bytes >= 0, "peer_copy: null pointer or negative size");
+    if (bytes == 0) return TC_OK;
+    TCB_CUDA(cudaMemcpyAsync(dst, src, static_cast<size_t>(bytes), cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+    return TC_OK;
+}
+
 }  // extern "C"

@@ -156,6 +156,82 @@ def exchange_row_block(full: torch.Tensor, ranges, lo: int, hi: int, group=None)
     return dist.batch_isend_irecv(ops_list) if ops_list else []
 
 
+class PeerWindows:
+    """The same tensor of every rank of the box, writable from this rank (one process per GPU, all GPUs of the box
+    visible to every process). Each rank exports the device allocation its tensor lies in (tc_peer_export) and opens
+    the others' with its own GPU current (tc_peer_open), which maps them with peer access over NVLink. A push is
+    a device-to-device cudaMemcpyAsync from local memory into a peer's window: it runs on the copy engines and
+    takes no SM from the kernels that run beside it. The exporting rank must keep its tensor alive while any rank
+    still holds a window on it."""
+
+    HANDLE_BYTES = 64
+
+    def __init__(self, tensor: torch.Tensor, group=None):
+        import ctypes
+
+        from . import _lib
+
+        if not tensor.is_contiguous():
+            raise ValueError("peer windows need a contiguous tensor")
+        self.lib = _lib.load()
+        self.check = _lib.check
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.group = group
+        self.tensor = tensor
+        self.key = (tensor.data_ptr(), tuple(tensor.shape))
+        # offset of the tensor inside its device allocation (the caching allocator's segment)
+        base_addr = None
+        for seg in torch.cuda.memory_snapshot():
+            if seg["device"] == tensor.device.index and seg["address"] <= tensor.data_ptr() < seg["address"] + seg["total_size"]:
+                base_addr = seg["address"]
+        if base_addr is None:
+            raise RuntimeError("the tensor does not lie in a device allocation of this process's caching allocator")
+        offset = tensor.data_ptr() - base_addr
+        handle = ctypes.create_string_buffer(self.HANDLE_BYTES)
+        with torch.cuda.device(tensor.device):
+            self.check("tc_peer_export", self.lib.tc_peer_export(ctypes.c_void_p(base_addr), handle, self.HANDLE_BYTES))
+            exported = [None] * self.world
+            dist.all_gather_object(exported, (handle.raw, offset), group=group)
+            self.bases = [None] * self.world
+            self.ptrs = [None] * self.world
+            for r, (raw, off) in enumerate(exported):
+                if r == self.rank:
+                    self.ptrs[r] = tensor.data_ptr()
+                    continue
+                base = ctypes.c_void_p()
+                self.check("tc_peer_open", self.lib.tc_peer_open(ctypes.create_string_buffer(raw, self.HANDLE_BYTES), self.HANDLE_BYTES,
+                                                                 ctypes.byref(base)))
+                self.bases[r] = base.value
+                self.ptrs[r] = base.value + off
+        self.flag = torch.zeros(1, device=tensor.device)
+        self.row_bytes = tensor.stride(0) * tensor.element_size()
+
+    def push_rows(self, lo: int, hi: int) -> None:
+        """Copies rows [lo, hi) of this rank's tensor into the same rows of every peer's, on the current stream.
+        Peer (rank + s) is served in slot s, so that in every slot each GPU receives from exactly one sender."""
+        import ctypes
+
+        stream = ctypes.c_void_p(torch.cuda.current_stream(self.tensor.device).cuda_stream)
+        off, nbytes = lo * self.row_bytes, (hi - lo) * self.row_bytes
+        for step in range(1, self.world):
+            peer = (self.rank + step) % self.world
+            self.check("tc_peer_copy", self.lib.tc_peer_copy(ctypes.c_void_p(self.ptrs[peer] + off),
+                                                             ctypes.c_void_p(self.ptrs[self.rank] + off), nbytes, stream))
+
+    def fence(self) -> None:
+        """Orders the current stream after every rank's pushes that precede ITS fence: a one-element all-reduce,
+        which no rank's stream passes before all ranks' streams have reached it."""
+        dist.all_reduce(self.flag, group=self.group)
+
+    def close(self) -> None:
+        import ctypes
+
+        for r, base in enumerate(self.bases):
+            if base is not None:
+                self.lib.tc_peer_close(ctypes.c_void_p(base))
+                self.bases[r] = None
+
+
 class OverlappedGemm:
     """c = a @ b.T with the rows of a (and c) split across ranks and C assembled on every rank WHILE it is computed:
     a rank's slab is cut into row blocks, each block's GEMM runs on the caller's stream on `max_sms` SMs, and as soon
@@ -164,10 +240,17 @@ class OverlappedGemm:
     GEMM. Slabs must be equal and divisible into `blocks` blocks of whole 128-row tiles; otherwise the gather
     follows the compute (all_gather_slabs)."""
 
-    def __init__(self, blocks: int = 4, max_sms: int = 0):
+    def __init__(self, blocks: int = 4, max_sms: int = 0, transport: str = "nccl"):
+        """transport "nccl": grouped send / receive per block (needs SMs: give the GEMM a budget with max_sms);
+        "copy_engine": every rank pushes its finished block into the other ranks' C through CUDA IPC windows
+        (PeerWindows), which takes no SM, so the GEMM keeps them all; C must then be the same tensor on every call."""
+        if transport not in ("nccl", "copy_engine"):
+            raise ValueError("transport must be 'nccl' or 'copy_engine'")
         self.blocks = blocks
         self.max_sms = max_sms
+        self.transport = transport
         self.side = None
+        self.windows = None
 
     def __call__(self, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, gather: bool = True, group=None) -> Tuple[int, int]:
         from . import ops
@@ -191,6 +274,22 @@ class OverlappedGemm:
             self.side = torch.cuda.Stream(device=c.device)
         main = torch.cuda.current_stream(c.device)
         per = rows // self.blocks
+        if self.transport == "copy_engine":
+            if self.windows is None or self.windows.key != (c.data_ptr(), tuple(c.shape)):
+                if self.windows is not None:
+                    self.windows.close()
+                self.windows = PeerWindows(c, group)
+            for j in range(self.blocks):
+                lo, hi = start + j * per, start + (j + 1) * per
+                ops.gemm(a[lo:hi], b, c[lo:hi], max_sms=self.max_sms)
+                done = torch.cuda.Event()
+                done.record(main)
+                self.side.wait_event(done)
+                with torch.cuda.stream(self.side):
+                    self.windows.push_rows(lo, hi)
+            main.wait_stream(self.side)
+            self.windows.fence()    # every rank's blocks have arrived here once this completes
+            return start, stop
         works = []
         for j in range(self.blocks):
             lo, hi = j * per, (j + 1) * per
