@@ -799,6 +799,9 @@ def reference_cuda_kernels() -> dict:
         "fused_two_gemms": {"unavailable": "the reference's example binary ended with 'CUDA Runtime Error ... misaligned address' "
                                            "(fused_gemm.cu:117) on B200 after failing its own check at its second configuration; "
                                            "not run again on this pool"},
+        "flash_attention": {"unavailable": "the reference's library kernel, run once on B200 through its own run_flash_attention at the "
+                                           "largest shape its launcher supports (m 64, n 256, k = p = 128), ended with 'misaligned address'; "
+                                           "not run again on this pool"},
         "scatter_nd": {"unavailable": "launcher defect in the reference: its launch passes the index buffer where the kernel expects "
                                       "the update values (src/kernels/scatter_nd.cu:107), so its result is not the op's"},
         "lstm_cell": {"unavailable": "the reference snapshot names the op (Makefile:3) but has no code for it"},
@@ -905,16 +908,18 @@ def strong_gemm_leg(device, rank: int, world: int, barrier, reduce_max, steps: i
     serial_ms = reduce_max(time_steps(lambda: shard.sharded_gemm(a, b, c, gather=True), steps, 3, barrier))
     best = None
     tried = []
-    for transport, blocks, max_sms in (("copy_engine", 4, 0), ("copy_engine", 8, 0), ("nccl", 4, 132), ("nccl", 8, 132)):
+    for transport, blocks, max_sms, copy_streams in (("copy_engine", 4, 0, 4), ("copy_engine", 4, 0, 7), ("copy_engine", 4, 0, 1),
+                                                    ("copy_engine", 2, 0, 4), ("nccl", 4, 132, 0)):
         if (stop - start) % (blocks * 128) != 0:
             continue
         try:
-            op = shard.OverlappedGemm(blocks=blocks, max_sms=max_sms, transport=transport)
+            op = shard.OverlappedGemm(blocks=blocks, max_sms=max_sms, transport=transport, copy_streams=copy_streams)
             ms = reduce_max(time_steps(lambda: op(a, b, c), steps, 3, barrier))
         except RuntimeError as e:   # CUDA IPC refused (a sandbox may not allow it): the NCCL transport remains
             tried.append({"transport": transport, "blocks": blocks, "unavailable": str(e)[:160]})
             continue
-        tried.append({"transport": transport, "blocks": blocks, "gemm_sms": max_sms or "all", "ms": round(ms, 4)})
+        tried.append({"transport": transport, "blocks": blocks, "gemm_sms": max_sms or "all",
+                      **({"copy_streams": min(copy_streams, world - 1)} if transport == "copy_engine" else {}), "ms": round(ms, 4)})
         if best is None or ms < best[0]:
             best = (ms, blocks, max_sms, transport)
     # the assembled C of the last (overlapped) run against the product computed by one GPU: exact equality,

@@ -206,15 +206,19 @@ class PeerWindows:
         self.flag = torch.zeros(1, device=tensor.device)
         self.row_bytes = tensor.stride(0) * tensor.element_size()
 
-    def push_rows(self, lo: int, hi: int) -> None:
-        """Copies rows [lo, hi) of this rank's tensor into the same rows of every peer's, on the current stream.
-        Peer (rank + s) is served in slot s, so that in every slot each GPU receives from exactly one sender."""
+    def push_rows(self, lo: int, hi: int, streams=None) -> None:
+        """Copies rows [lo, hi) of this rank's tensor into the same rows of every peer's. Peer (rank + s) is served in
+        slot s, so that in every slot each GPU receives from exactly one sender. The copies go to `streams` in turn
+        (the current stream if none is given): copies on different streams run on different copy engines at once,
+        which one stream's queue of copies, each to another peer, does not."""
         import ctypes
 
-        stream = ctypes.c_void_p(torch.cuda.current_stream(self.tensor.device).cuda_stream)
+        if not streams:
+            streams = [torch.cuda.current_stream(self.tensor.device)]
         off, nbytes = lo * self.row_bytes, (hi - lo) * self.row_bytes
         for step in range(1, self.world):
             peer = (self.rank + step) % self.world
+            stream = ctypes.c_void_p(streams[(step - 1) % len(streams)].cuda_stream)
             self.check("tc_peer_copy", self.lib.tc_peer_copy(ctypes.c_void_p(self.ptrs[peer] + off),
                                                              ctypes.c_void_p(self.ptrs[self.rank] + off), nbytes, stream))
 
@@ -240,7 +244,7 @@ class OverlappedGemm:
     GEMM. Slabs must be equal and divisible into `blocks` blocks of whole 128-row tiles; otherwise the gather
     follows the compute (all_gather_slabs)."""
 
-    def __init__(self, blocks: int = 4, max_sms: int = 0, transport: str = "nccl"):
+    def __init__(self, blocks: int = 4, max_sms: int = 0, transport: str = "nccl", copy_streams: int = 4):
         """transport "nccl": grouped send / receive per block (needs SMs: give the GEMM a budget with max_sms);
         "copy_engine": every rank pushes its finished block into the other ranks' C through CUDA IPC windows
         (PeerWindows), which takes no SM, so the GEMM keeps them all; C must then be the same tensor on every call."""
@@ -251,6 +255,8 @@ class OverlappedGemm:
         self.transport = transport
         self.side = None
         self.windows = None
+        self.copy_streams = max(1, copy_streams)
+        self.pushers = None
 
     def __call__(self, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, gather: bool = True, group=None) -> Tuple[int, int]:
         from . import ops
@@ -279,15 +285,18 @@ class OverlappedGemm:
                 if self.windows is not None:
                     self.windows.close()
                 self.windows = PeerWindows(c, group)
+            if self.pushers is None:
+                self.pushers = [torch.cuda.Stream(device=c.device) for _ in range(min(self.copy_streams, world - 1))]
             for j in range(self.blocks):
                 lo, hi = start + j * per, start + (j + 1) * per
                 ops.gemm(a[lo:hi], b, c[lo:hi], max_sms=self.max_sms)
                 done = torch.cuda.Event()
                 done.record(main)
-                self.side.wait_event(done)
-                with torch.cuda.stream(self.side):
-                    self.windows.push_rows(lo, hi)
-            main.wait_stream(self.side)
+                for s in self.pushers:
+                    s.wait_event(done)
+                self.windows.push_rows(lo, hi, self.pushers)
+            for s in self.pushers:
+                main.wait_stream(s)
             self.windows.fence()    # every rank's blocks have arrived here once this completes
             return start, stop
         works = []
