@@ -82,6 +82,19 @@ def test_static_chain_refuses_sizes_beyond_its_built_in_scratch_without_a_device
         assert "built into" in lib.tc_last_error().decode()
 
 
+def test_peer_window_and_sm_budget_argument_checks():
+    lib = _lib.load()
+    buf = ctypes.create_string_buffer(64)
+    assert lib.tc_peer_export(None, buf, 64) == -1 and "null" in lib.tc_last_error().decode()
+    assert lib.tc_peer_export(16, buf, 8) == -1 and "handle buffer" in lib.tc_last_error().decode()
+    out = ctypes.c_void_p()
+    assert lib.tc_peer_open(buf, 8, ctypes.byref(out)) == -1
+    assert lib.tc_peer_copy(None, 16, 4, None) == -1
+    assert lib.tc_peer_close(None) == 0
+    assert lib.tc_gemm_f16_f32_sms(16, 16, 16, 128, 128, 64, 64, 64, 128, -3, None) == -1 and "max_sms" in lib.tc_last_error().decode()
+    assert lib.tc_gemm_f16_f32_sms(16, 16, 16, 128, 128, 64, 64, 64, 128, 1, None) == -1
+
+
 def test_scatter_argument_checks():
     lib = _lib.load()
     dims = (ctypes.c_int64 * 2)(8, 4)

@@ -83,6 +83,20 @@ def test_gemm_guard_bands_aligned_and_unaligned_output(cuda_ops, clean_status, c
     assert (guard == -7.0).all(), "GEMM wrote outside its output"
 
 
+@pytest.mark.parametrize("max_sms", [140, 132, 64, 2])
+def test_gemm_on_an_sm_budget_gives_the_same_result(cuda_ops, clean_status, max_sms):
+    """tc_gemm_f16_f32_sms sizes the tile plan and the persistent grid for the budget; the result is the one of the
+    unrestricted call (compared with the oracle, and bit for bit where both calls take the same tile shape)."""
+    m, n, k = 4000, 4090, 520
+    a, b = oracle.gemm_inputs(m, n, k)
+    a_dev, b_dev = a.to(DEV), b.to(DEV)
+    full, part = torch.empty(m, n, device=DEV), torch.full((m, n), float("nan"), device=DEV)
+    cuda_ops.gemm(a_dev, b_dev, full)
+    cuda_ops.gemm(a_dev, b_dev, part, max_sms=max_sms)
+    assert_close(part, oracle.gemm(a, b), max_abs=2e-3, rel_fro=1e-5)
+    assert torch.equal(part, full)   # every tile shape accumulates K in the same order
+
+
 def test_gemm_linearity_at_sweep_size(cuda_ops, clean_status):
     """Size-independent property at 4096^3: (A1 + A2) B^T = A1 B^T + A2 B^T when the sum is exact in fp16."""
     n = 4096
