@@ -908,8 +908,8 @@ def strong_gemm_leg(device, rank: int, world: int, barrier, reduce_max, steps: i
     serial_ms = reduce_max(time_steps(lambda: shard.sharded_gemm(a, b, c, gather=True), steps, 3, barrier))
     best = None
     tried = []
-    for transport, blocks, max_sms, copy_streams in (("copy_engine", 4, 0, 4), ("copy_engine", 4, 0, 7), ("copy_engine", 4, 0, 1),
-                                                    ("copy_engine", 2, 0, 4), ("nccl", 4, 132, 0)):
+    for transport, blocks, max_sms, copy_streams in (("copy_engine", 4, 0, 1), ("copy_engine", 8, 0, 1), ("copy_engine", 4, 0, 2),
+                                                    ("nccl", 4, 132, 0)):
         if (stop - start) % (blocks * 128) != 0:
             continue
         try:
@@ -918,6 +918,10 @@ def strong_gemm_leg(device, rank: int, world: int, barrier, reduce_max, steps: i
         except RuntimeError as e:   # CUDA IPC refused (a sandbox may not allow it): the NCCL transport remains
             tried.append({"transport": transport, "blocks": blocks, "unavailable": str(e)[:160]})
             continue
+        if op.assembly is not None and op.assembly.windows is not None:
+            torch.cuda.synchronize()
+            op.assembly.windows.close()     # no rank keeps a window on C beyond this leg (C is freed below)
+            barrier()
         tried.append({"transport": transport, "blocks": blocks, "gemm_sms": max_sms or "all",
                       **({"copy_streams": min(copy_streams, world - 1)} if transport == "copy_engine" else {}), "ms": round(ms, 4)})
         if best is None or ms < best[0]:
@@ -975,10 +979,24 @@ def sharded_others(device, rank: int, world: int, barrier, reduce_max) -> dict:
     pairs = fa.batch * fa.heads
     lo, hi = shard.shard_range(pairs, world, rank)
     gather_ms = reduce_max(time_steps(lambda: shard.all_gather_slabs(fa.o.view(pairs, fa.seq, fa.dim), world, rank), 5, 2, barrier))
+    serial_ms = reduce_max(time_steps(lambda: shard.sharded_flash_attn(fa.q, fa.k, fa.v, fa.o, gather=True), 10, 3, barrier))
     out["fa"] = {"units": f"{pairs} (batch, head) pairs, {hi - lo} on this rank", "ms_sharded": round(ms, 4), "single_gpu_ms": round(single, 4),
                  "tflops_per_gpu": round(fa.units_per_step() / world / (ms * 1e-3) / 1e12, 1),
                  "efficiency": round(single / (world * ms), 4), "gather_of_O_ms": round(gather_ms, 4),
+                 "ms_then_gather": round(serial_ms, 4),
                  "bound_by": "compute; the fp16 O all-gather (timed apart) is NVLink-ingress bound"}
+    try:
+        asm = shard.OverlappedAssembly(blocks=4)
+        ov_ms = reduce_max(time_steps(lambda: shard.overlapped_flash_attn(asm, fa.q, fa.k, fa.v, fa.o), 10, 3, barrier))
+        out["fa"].update({"ms_with_O_assembled_overlapped": round(ov_ms, 4),
+                          "efficiency_with_O_assembled": round(single / (world * ov_ms), 4),
+                          "overlap": "finished (batch, head) groups pushed into the peers' O by the copy engines (peer windows) "
+                                     "while later groups are computed"})
+        torch.cuda.synchronize()
+        asm.windows.close()
+        barrier()
+    except RuntimeError as e:
+        out["fa"]["overlap_unavailable"] = str(e)[:160]
     del fa
     torch.cuda.empty_cache()
 

@@ -194,7 +194,8 @@ int tc_scatter_nd_add(void* data, const void* updates, const void* indices, int 
  * address of that allocation as seen from the opener (add the exported pointer's offset inside its allocation);
  * an allocation can be opened once per process. tc_peer_copy queues a device-to-device copy on `stream`; ordering
  * against the owner's own kernels is the caller's business (a collective or an event shared by the ranks).
- * tc_peer_close unmaps a window. The reference is single-GPU and single-process; these have no counterpart there. */
+ * tc_peer_close unmaps a window; every rank closes its windows on a buffer before the owner frees it. The reference is
+ * single-GPU and single-process; these have no counterpart there. */
 #define TC_PEER_HANDLE_BYTES 64
 int tc_peer_export(const void* dev_ptr, void* handle_out, int64_t handle_bytes);
 int tc_peer_open(const void* handle, int64_t handle_bytes, void** base_out);

@@ -52,6 +52,8 @@ def _worker(rank, world, port, q):
         push(a_d, b_d, c3)                   # second call: the windows are reused
         torch.cuda.synchronize()
         ok["gemm_overlapped_copy_engine_again"] = bool(torch.equal(c3, c))
+        push.assembly.windows.close()        # windows are closed before their tensors are freed
+        dist.barrier()
 
         # the host-operand pipeline: own A slab and half of B from the host, B gathered over NVLink
         pipe = shard.HostGemmPipeline(1024, 640, 512, dev, blocks=4)
@@ -67,6 +69,13 @@ def _worker(rank, world, port, q):
         shard.sharded_flash_attn(q_.to(dev), k_.to(dev), v_.to(dev), o, gather=True)
         torch.cuda.synchronize()
         ok["fa"] = oracle.within_tolerance(o, oracle.flash_attention(q_, k_, v_)[0])
+        o2 = torch.full((2, 3, 256, 64), float("nan"), dtype=torch.float16, device=dev)
+        assembly = shard.OverlappedAssembly(blocks=2)
+        shard.overlapped_flash_attn(assembly, q_.to(dev), k_.to(dev), v_.to(dev), o2)
+        torch.cuda.synchronize()
+        ok["fa_overlapped"] = bool(torch.equal(o2, o))
+        assembly.windows.close()
+        dist.barrier()
 
         # LSTM chain over batch rows
         w, u, bias, x, h0, c0 = oracle.lstm_inputs(5, 192, 128, 64, with_bias=True)
