@@ -305,6 +305,36 @@ def test_flash_attn_seq_major_operands(cuda_ops, clean_status, causal, b, h, sq,
         assert torch.equal(o.transpose(1, 2), o2)
 
 
+@pytest.mark.parametrize(
+    "b,h,sq,skv,d,dv,vt,seq_major",
+    [
+        (4, 40, 512, 320, 64, 64, False, False),     # 320 CTAs on 148 SMs, an odd number of half blocks per CTA
+        (2, 80, 456, 1000, 128, 128, False, False),  # ragged query tail (second tile partly outside) and ragged KV tail
+        (3, 50, 512, 256, 128, 128, True, False),    # V given transposed
+        (2, 96, 256, 128, 64, 128, False, True),     # one query block per head, sequence-major operands, two half blocks
+        (1, 160, 256, 64, 128, 128, False, False),   # a single half block per CTA
+    ],
+)
+def test_flash_attn_more_ctas_than_sms_matches_oracle(cuda_ops, clean_status, b, h, sq, skv, d, dv, vt, seq_major):
+    """Non-causal attention with more (batch x head, query block) CTAs than SMs, so that SMs take several CTAs in
+    turn: odd and single half-block counts, ragged query and KV tails, transposed V, sequence-major operands. Output
+    and LSE of every (batch, head) against the oracle."""
+    q, k, v = oracle.attention_inputs(b, h, sq, skv, d, dv)
+    lse = torch.empty(b, h, sq, device=DEV)
+    ref, ref_lse = oracle.flash_attention(q, k, v)
+    if seq_major:
+        to_sm = lambda t: t.to(DEV).transpose(1, 2).contiguous()
+        o = torch.full((b, sq, h, dv), float("nan"), dtype=torch.float16, device=DEV)
+        cuda_ops.flash_attn(to_sm(q), to_sm(k), to_sm(v), o, lse=lse, seq_major=True)
+        o = o.transpose(1, 2)
+    else:
+        o = torch.full((b, h, sq, dv), float("nan"), dtype=torch.float16, device=DEV)
+        vd = v.to(DEV).transpose(2, 3).contiguous() if vt else v.to(DEV)
+        cuda_ops.flash_attn(q.to(DEV), k.to(DEV), vd, o, lse=lse, v_is_transposed=vt)
+    assert_close(o, ref)
+    assert (lse.cpu() - ref_lse).abs().max().item() < 1e-3
+
+
 def test_flash_attn_ex_rejects_bad_combinations(cuda_ops, clean_status):
     q = torch.zeros(1, 64, 2, 64, dtype=torch.float16, device=DEV)
     with pytest.raises(ValueError):
