@@ -57,7 +57,7 @@ struct AttnParams {
 template <bool kVTrans>
 __global__ void __launch_bounds__(kFaThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+                const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o, const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align_smem_1024(smem_raw);
     uint8_t* s_q = smem;                   // two Q tiles
@@ -367,27 +367,41 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
 
         // ---------------- epilogue ----------------
-        if (ok && mbar_wait_warp(&bar_o_full[t], 0, abort_word, kDevTimeoutEpilogue)) {
+        // The normalised rows go through shared memory and leave as TMA stores of whole 128-byte lines: the Q tile of
+        // this warpgroup's tile has been read by its last score MMA long before the last P V product completes, so its
+        // 32 KiB (128 rows x 256 bytes, the 128-byte-swizzled box layout of the output map) serve as staging. Rows and
+        // columns outside the output are clipped by TMA.
+        const bool o_ready = ok && mbar_wait_warp(&bar_o_full[t], 0, abort_word, kDevTimeoutEpilogue);
+        if (o_ready) {
             tc_fence_after_sync();
             const float inv_l = l_sum > 0.f ? 1.f / l_sum : 0.f;   // a fully masked row yields zeros
-            const int64_t out_row = static_cast<int64_t>(bh) * p.seq_q + row;
-            __half* out_ptr = p.out + bat * p.out_stride_b + head * p.out_stride_h + row * p.out_stride_s;
+            const int r_in_tile = quarter * 32 + lane;
+            uint8_t* stage_row = s_q + t * kFaTile + r_in_tile * 128;
 #pragma unroll 1
             for (int c = 0; c < p.dv / 16; ++c) {
                 uint32_t r[16];
                 tmem_ld_x16(o_addr + static_cast<uint32_t>(c * 16), r);
                 tmem_ld_wait();
-                if (row < p.seq_q) {
-                    uint32_t h[8];
+                uint32_t h[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        h[i] = pack_half2(__uint_as_float(r[2 * i]) * inv_l, __uint_as_float(r[2 * i + 1]) * inv_l);
-                    uint4* dst = reinterpret_cast<uint4*>(out_ptr + c * 16);
-                    dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
-                    dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
-                }
+                for (int i = 0; i < 8; ++i)
+                    h[i] = pack_half2(__uint_as_float(r[2 * i]) * inv_l, __uint_as_float(r[2 * i + 1]) * inv_l);
+                uint8_t* chunk = stage_row + (c >> 2) * kFaChunk;      // 64 output columns per 16 KiB chunk
+                const int piece = (c & 3) * 2;                           // 16-byte pieces of this row inside the chunk
+                *reinterpret_cast<uint4*>(chunk + (((piece) ^ (r_in_tile & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+                *reinterpret_cast<uint4*>(chunk + (((piece + 1) ^ (r_in_tile & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
             }
-            if (p.lse != nullptr && row < p.seq_q) p.lse[out_row] = (m_used + log2f(l_sum)) * 0.6931471805599453f;
+            if (p.lse != nullptr && row < p.seq_q)
+                p.lse[static_cast<int64_t>(bh) * p.seq_q + row] = (m_used + log2f(l_sum)) * 0.6931471805599453f;
+            fence_proxy_async_smem();
+        }
+        // all four warps of the tile have staged their rows (or given up) before one thread hands the tile to TMA
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + t) : "memory");
+        if (o_ready && quarter == 0 && lane == 0 && q0 + t * kFaBM < p.seq_q) {
+            for (int c = 0; c < v_chunks; ++c)
+                tma_store_4d(&tmap_o, s_q + t * kFaTile + c * kFaChunk, c * 64, q0 + t * kFaBM, head, bat);
+            tma_store_commit();
+            tma_store_wait<0>();   // the tile has left shared memory and reached the output before the CTA may exit
         }
     }
 
@@ -446,14 +460,17 @@ int launch_attn_pingpong(const void* Q, const void* K, const void* V, void* O, f
     p.out = static_cast<__half*>(O);
     p.lse = lse;
     p.status = dev->status_word;
+    // the output as the input maps see their tensors: [batch, heads, seq_q, dv] or, sequence-major, [batch, seq_q, heads, dv]
+    CUtensorMap to;
+    if (int rc = encode(&to, O, seq_q, dv, kFaBM)) return rc;
     const dim3 grid(static_cast<unsigned>((seq_q + 2 * kFaBM - 1) / (2 * kFaBM)), static_cast<unsigned>(batch * heads));
     static OncePerDevice once[2];
     if (v_trans) {
         if (int rc = raise_smem_limit_once(once[1], dev->device, attn_fwd_kernel<true>, kFaSmem)) return rc;
-        attn_fwd_kernel<true><<<grid, kFaThreads, kFaSmem, stream>>>(tq, tk, tv, p);
+        attn_fwd_kernel<true><<<grid, kFaThreads, kFaSmem, stream>>>(tq, tk, tv, to, p);
     } else {
         if (int rc = raise_smem_limit_once(once[0], dev->device, attn_fwd_kernel<false>, kFaSmem)) return rc;
-        attn_fwd_kernel<false><<<grid, kFaThreads, kFaSmem, stream>>>(tq, tk, tv, p);
+        attn_fwd_kernel<false><<<grid, kFaThreads, kFaSmem, stream>>>(tq, tk, tv, to, p);
     }
     TCB_CUDA(cudaGetLastError());
     return TC_OK;
