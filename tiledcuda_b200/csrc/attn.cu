@@ -54,6 +54,78 @@ struct AttnParams {
     uint32_t* status;
 };
 
+struct SoftmaxState {
+    float m;   // reference maximum of the row (in units of log2, scale folded in)
+    float l;   // sum of the row's exponentials against that reference
+    bool ok;
+};
+
+// One half block of one query row per thread, the general way: the first half block of a tile (no reference yet),
+// half blocks with masked columns (end of the sequence, causal diagonal), and half blocks in which some row of the
+// warp outgrew its reference by more than 2^8. Whole warps call it. Reads the 64 scores at s_addr, raises the
+// reference where needed (then O is rescaled, after `bar_pv` says that no product into it is in flight), writes the
+// fp16 probabilities over the scores and returns the updated row state. Not inlined: it holds its own copy of the
+// exponentials and is kept out of the loop that runs for every other half block.
+static __device__ __noinline__ SoftmaxState softmax_half_block_general(uint32_t s_addr, uint32_t o_addr, int n_valid, float sc,
+                                                                       int o_chunks, bool first, uint64_t* bar_pv,
+                                                                       uint32_t bar_pv_parity, volatile uint32_t* abort_word,
+                                                                       float m_used, float l_sum) {
+    uint32_t s[64];
+    tmem_ld_x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+    tmem_ld_x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+    tmem_ld_wait();
+    // scaled scores, masked columns at -inf (after scaling, so that a scale of zero masks too)
+    float row_max = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+        const float x = i < n_valid ? __uint_as_float(s[i]) * sc : -INFINITY;
+        s[i] = __float_as_uint(x);
+        row_max = fmaxf(row_max, x);
+    }
+    float factor = 1.f;
+    bool raised = false;
+    if (first) {
+        m_used = fmaxf(row_max, -1e30f);   // finite even for a row that sees no KV row at all
+    } else if (row_max - m_used > kFaRescaleThreshold) {
+        factor = fast_exp2(m_used - row_max);
+        m_used = row_max;
+        raised = true;
+    }
+    bool ok = true;
+    if (__any_sync(0xffffffffu, raised)) {
+        l_sum *= factor;
+        ok = mbar_wait_warp(bar_pv, bar_pv_parity, abort_word, kDevTimeoutSoftmax);
+        if (ok) {
+            tc_fence_after_sync();
+#pragma unroll 1
+            for (int c = 0; c < o_chunks; ++c) {
+                uint32_t r[16];
+                tmem_ld_x16(o_addr + static_cast<uint32_t>(c * 16), r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
+                tmem_st_x16(o_addr + static_cast<uint32_t>(c * 16), r);
+            }
+        }
+    }
+    if (ok) {
+        uint32_t pk[32];
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const float a = fast_exp2(__uint_as_float(s[2 * i]) - m_used);
+            const float b = fast_exp2(__uint_as_float(s[2 * i + 1]) - m_used);
+            sum0 += a;
+            sum1 += b;
+            pk[i] = pack_half2(a, b);
+        }
+        tmem_st_x32(s_addr, pk);
+        l_sum += sum0 + sum1;
+        tmem_st_wait();
+    }
+    return SoftmaxState{m_used, l_sum, ok};
+}
+
 template <bool kVTrans>
 __global__ void __launch_bounds__(kFaThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -98,11 +170,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
         for (int i = 0; i < 4; ++i) {
             mbar_init(&bar_s_full[i], 1);
-            mbar_init(&bar_p_full[i], 4);
+            mbar_init(&bar_p_full[i], 5);   // four softmax warps and the forwarder (warp 3)
         }
         for (int s = 0; s < kFaStages; ++s) {
             mbar_init(&bar_kv_full[s], 1);
-            mbar_init(&bar_kv_empty[s], two_tiles ? 2 : 1);  // one release per MMA warp in use
+            mbar_init(&bar_kv_empty[s], two_tiles ? 2 : 1);  // one release per tile in use (its softmax warpgroup)
         }
         *abort_word = 0;
         fence_barrier_init();
@@ -208,7 +280,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                         umma_f16_ts(tmem_o, a + static_cast<uint32_t>(kk * 8),
                                     smem_desc_join(b_lo + static_cast<uint32_t>(kk) * v_k_step, desc_hi), idesc_o, (g | kk) != 0);
                 }
-                if (leader) umma_commit(&bar_pv_done[t]);
             };
 
             // prologue: the first two half blocks of scores (both from K_0)
@@ -218,40 +289,49 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 tc_fence_after_sync();
                 issue_s(0);
                 if (n_halves > 1) issue_s(1);
-                if (leader) umma_commit(&bar_kv_empty[kv_stage(0)]);
             }
-            // The K / V barriers that an even half block needs are awaited at the end of the iteration before it:
-            // they have long completed by then, but even a completed wait costs the issuing thread a couple of
-            // hundred cycles, and there it overlaps the softmax instead of delaying the MMAs behind P.
-            auto await_kv = [&](int g) -> bool {
-                if ((g & 1) != 0 || g >= n_halves) return true;
-                const int j = g >> 1;
-                if (!mbar_wait(&bar_kv_full[kv_stage(2 * j + 1)], kv_phase(2 * j + 1), abort_word, kDevTimeoutMma)) return false;
-                return g + 2 >= n_halves ||
-                       mbar_wait(&bar_kv_full[kv_stage(2 * j + 2)], kv_phase(2 * j + 2), abort_word, kDevTimeoutMma);
-            };
-            ok = ok && await_kv(0);
+            // Every barrier operation between two MMAs of this thread is a bubble in the tensor pipe, whose queue runs
+            // barely an MMA or two behind the issuing thread (measured: 30 to 65 cycles per commit, 55 per wait that
+            // succeeds at once). So the loop holds one wait and one commit per half block: p_full also stands for "the
+            // K / V tiles of this step have landed" (warp 3 forwards that), the ring stages are released by the softmax
+            // warps when they see the scores that were issued behind the last MMA reading a stage, and the completion of
+            // a P V product is read off the scores issued behind it.
             for (int g = 0; ok && g < n_halves; ++g) {
-                const int j = g >> 1;
                 const bool more_s = g + 2 < n_halves;
                 if (!mbar_wait(&bar_p_full[t * 2 + (g & 1)], static_cast<uint32_t>((g >> 1) & 1), abort_word, kDevTimeoutMma)) break;
                 tc_fence_after_sync();
                 issue_pv(g);
-                if (more_s) issue_s(g + 2);
-                if (leader) {
-                    if (g == n_halves - 1) umma_commit(&bar_o_full[t]);
-                    // V_j is free once its second half (or the last half block) has been issued
-                    if ((g & 1) == 1 || g == n_halves - 1) umma_commit(&bar_kv_empty[kv_stage(2 * j + 1)]);
-                    // K of block (g+2)/2 is free once its last half block of scores has been issued
-                    if (more_s && (((g + 2) & 1) == 1 || g + 2 == n_halves - 1))
-                        umma_commit(&bar_kv_empty[kv_stage(2 * ((g + 2) >> 1))]);
-                }
-                if (!await_kv(g + 1)) break;
+                if (more_s) issue_s(g + 2);   // commits to s_full
+                if (g == n_halves - 2) umma_commit(&bar_pv_done[t]);   // no scores follow this product
+                if (g == n_halves - 1) umma_commit(&bar_o_full[t]);
             }
         }
         __syncwarp();
     } else if (warp == 3) {
-        // idle: keeps the softmax warpgroups aligned to TMEM lane quarters
+        // ---------------- forwarder ----------------
+        // Adds "the tiles the issuers need at half block g have landed" to p_full of half block g as its fifth arrival:
+        // V of block g / 2 for P(g) V and K of block (g + 2) / 2 for the scores of half block g + 2, both new at even g.
+        // An arrival counts for the barrier's current phase, so the one for g waits until the phase of g - 2 is complete.
+        if (lane == 0) {
+            auto kv_stage = [](int e) { return e % kFaStages; };
+            auto kv_phase = [](int e) { return static_cast<uint32_t>((e / kFaStages) & 1); };
+            const int n_tiles = two_tiles ? 2 : 1;
+            bool ok = true;
+            for (int g = 0; ok && g < n_halves; ++g) {
+                if ((g & 1) == 0) {
+                    const int j = g >> 1;
+                    ok = mbar_wait(&bar_kv_full[kv_stage(2 * j + 1)], kv_phase(2 * j + 1), abort_word, kDevTimeoutMma) &&
+                         (g + 2 >= n_halves ||
+                          mbar_wait(&bar_kv_full[kv_stage(2 * j + 2)], kv_phase(2 * j + 2), abort_word, kDevTimeoutMma));
+                }
+                for (int t = 0; ok && t < n_tiles; ++t) {
+                    if (g >= 2)
+                        ok = mbar_wait(&bar_p_full[t * 2 + (g & 1)], static_cast<uint32_t>(((g - 2) >> 1) & 1), abort_word, kDevTimeoutMma);
+                    if (ok) mbar_arrive(&bar_p_full[t * 2 + (g & 1)]);
+                }
+            }
+        }
+        __syncwarp();
     } else {
         // ---------------- softmax warpgroups: one thread per query row ----------------
         const int t = (warp - 4) >> 2;   // tile of this warpgroup
@@ -264,7 +344,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         float m_used = -INFINITY;
         float l_sum = 0.f;
         bool ok = (t == 0) || two_tiles;
-
         for (int g = 0; ok && g < n_halves; ++g) {
             const int h = g & 1;
             if (!mbar_wait_warp(&bar_s_full[t * 2 + h], static_cast<uint32_t>((g >> 1) & 1), abort_word, kDevTimeoutSoftmax)) {
@@ -272,35 +351,40 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 break;
             }
             tc_fence_after_sync();
+            // The MMAs of one CTA complete in issue order: scores of half block g complete mean that K of block g / 2 has
+            // been read for this half, and that P(g-2) V, issued before them, has read its half of V.
+            if (quarter == 0 && lane == 0) {
+                if ((g & 1) == 1 || g == n_halves - 1) mbar_arrive(&bar_kv_empty[(2 * (g >> 1)) % kFaStages]);
+                if ((g & 1) == 1 && g >= 3) mbar_arrive(&bar_kv_empty[(2 * ((g - 2) >> 1) + 1) % kFaStages]);
+            }
             const uint32_t s_addr = s_base + static_cast<uint32_t>(h * 64);
             // columns of this half block the row may see: the end of the sequence and, with a causal mask, the diagonal
             int n_valid = min(64, p.seq_kv - g * 64);
             if (p.causal) n_valid = min(n_valid, row + p.causal_off + 1 - g * 64);
 
-            // the 64 scores of this row and half block into registers
-            uint32_t s[64];
-            tmem_ld_x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-            tmem_ld_x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-            tmem_ld_wait();
-            if (n_valid < 64) {
-                const float masked = sc >= 0.f ? -INFINITY : INFINITY;  // scale * masked = -inf
-#pragma unroll
-                for (int i = 0; i < 64; ++i)
-                    if (i >= n_valid) s[i] = __float_as_uint(masked);
-            }
-            // Exponentials are taken against the reference maximum m_used of the previous half blocks while the
-            // row extreme of this half block is still being reduced: the two are independent instruction
-            // streams (special-function unit against the ALU), and the reference only has to be replaced when
-            // some row outgrew it by 2^8, which after the first few half blocks is rare. When that happens
-            // the accumulator is rescaled and the exponentials are taken again from the scores, which are
-            // still in registers; the result is the same as reducing first.
-            uint32_t pk[32];
-            float sum0, sum1, sum2, sum3, r0, r1;
-            // x = scale * s - reference for all 64 scores, exp2(x) rounded to fp16 pairs, the partial sums, and (in
-            // the shadow of the exponentials, which leave most issue slots free) the largest x
-            auto exponentials = [&](float neg_m) {
-                sum0 = sum1 = sum2 = sum3 = 0.f;
-                r0 = r1 = -INFINITY;
+            // The common half block (not the first, no masked column in this warp) runs the short path below; everything
+            // else goes through softmax_half_block_general, a function of its own, so that the loop the eight softmax
+            // warps run 64 times per tile stays small in instruction memory.
+            // What the general path waits for before it rescales O_t, which may still be the target of P_t(g-1) V(g-1): the
+            // scores of half block g + 1 were issued behind that product (and do not depend on this half block), so their
+            // completion is its completion; behind the product before the last one the issuer commits to pv_done instead.
+            uint64_t* const bar_pv = g == n_halves - 1 ? &bar_pv_done[t] : &bar_s_full[t * 2 + ((g + 1) & 1)];
+            const uint32_t bar_pv_parity = g == n_halves - 1 ? 0u : static_cast<uint32_t>(((g + 1) >> 1) & 1);
+            bool general = g == 0 || __any_sync(0xffffffffu, n_valid < 64);
+            if (!general) {
+                // the 64 scores of this row and half block into registers
+                uint32_t s[64];
+                tmem_ld_x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+                tmem_ld_x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+                tmem_ld_wait();
+                // Exponentials are taken against the reference maximum m_used of the previous half blocks while the row
+                // extreme of this half block is still being reduced: the two are independent instruction streams
+                // (special-function unit against the ALU), and the reference only has to be replaced when some row
+                // outgrew it by 2^8, which after the first few half blocks is rare. Then the half block is done again
+                // by the general path from the scores, which are still in TMEM; the result is the same as reducing first.
+                uint32_t pk[32];
+                float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f, r0 = -INFINITY, r1 = -INFINITY;
+                const float neg_m = -m_used;
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     const float xa = fmaf(__uint_as_float(s[2 * i]), sc, neg_m);
@@ -320,47 +404,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     pk[i] = pack_half2(a, b);
                     pk[i + 1] = pack_half2(c2, d2);
                 }
-            };
-            float over;   // by how much the largest scaled score of this half block exceeds the reference
-            if (g == 0) {
-                exponentials(0.f);                            // first half block: only the maximum is used
-                m_used = fmaxf(fmaxf(r0, r1), -1e30f);        // finite even for a row that sees no KV row at all
-                exponentials(-m_used);
-                over = 0.f;
-            } else {
-                exponentials(-m_used);
-                over = fmaxf(r0, r1);
-            }
-            // the accumulator is rescaled only when some row of the warp outgrew its reference maximum by 2^8
-            const bool outgrown = __any_sync(0xffffffffu, over > kFaRescaleThreshold);
-            if (outgrown) {
-                float factor = 1.f;
-                if (over > kFaRescaleThreshold) {
-                    factor = fast_exp2(-over);
-                    m_used += over;
+                general = __any_sync(0xffffffffu, fmaxf(r0, r1) > kFaRescaleThreshold);
+                if (!general) {
+                    tmem_st_x32(s_addr, pk);
+                    l_sum += (sum0 + sum1) + (sum2 + sum3);
+                    tmem_st_wait();
                 }
-                l_sum *= factor;
-                // O_t may still be the target of P_t(g-1) V(g-1): wait for it. Seeing s_full of half block g
-                // means the product of half block g-2 is complete, so the parity is unambiguous.
-                if (!mbar_wait_warp(&bar_pv_done[t], static_cast<uint32_t>((g - 1) & 1), abort_word, kDevTimeoutSoftmax)) {
+            }
+            if (general) {
+                const SoftmaxState st = softmax_half_block_general(s_addr, o_addr, n_valid, sc, p.dv / 16, g == 0, bar_pv, bar_pv_parity,
+                                                                   abort_word, m_used, l_sum);
+                m_used = st.m;
+                l_sum = st.l;
+                if (!st.ok) {
                     ok = false;
                     break;
                 }
-                tc_fence_after_sync();
-#pragma unroll 1
-                for (int c = 0; c < p.dv / 16; ++c) {
-                    uint32_t r[16];
-                    tmem_ld_x16(o_addr + static_cast<uint32_t>(c * 16), r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
-                    tmem_st_x16(o_addr + static_cast<uint32_t>(c * 16), r);
-                }
             }
-            if (outgrown) exponentials(-m_used);
-            tmem_st_x32(s_addr, pk);
-            l_sum += (sum0 + sum1) + (sum2 + sum3);
-            tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_p_full[t * 2 + h]);
