@@ -145,7 +145,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_o_full + 2);
     volatile uint32_t* abort_word = tmem_slot + 1;
 
-    const int warp = threadIdx.x >> 5;
+    // broadcast from lane 0, so that the compiler knows the role of a warp to be the same for all its lanes
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
     const int lane = threadIdx.x & 31;
     // with a causal mask the CTAs with the most KV blocks are scheduled first
     const int q_blk = p.causal ? static_cast<int>(gridDim.x - 1 - blockIdx.x) : static_cast<int>(blockIdx.x);
@@ -232,11 +233,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         __syncwarp();
     } else if (warp == 1 || warp == 2) {
         // ---------------- MMA issuers: warp 1 drives tile 0, warp 2 drives tile 1 ----------------
-        // One lane runs the whole role: a commit tracks the MMAs of the thread that executes it, and a
-        // role that never re-converges with its idle lanes pays no divergence cost inside the loop.
+        // The whole warp runs the role and one elected lane executes the MMAs and their commits (a commit tracks the
+        // MMAs of the thread that executes it). With every lane on the same path the descriptor arithmetic stays in
+        // the uniform datapath, whose registers tcgen05.mma reads; behind a branch on the lane index every operand
+        // would first be moved there, which costs a fifth of the tensor pipe's time at these MMA sizes (measured:
+        // 1143 against 1261 cycles for the 24 MMAs of a half block of both tiles).
         const int t = warp - 1;
-        constexpr bool leader = true;
-        if (lane == 0 && (t == 0 || two_tiles)) {
+        if (t == 0 || two_tiles) {
+            const bool leader = elect_one_sync();
             const uint32_t idesc_s = make_idesc_f16_f32(kFaBM, 64, false, false);
             const uint32_t idesc_o = make_idesc_f16_f32(kFaBM, p.dv, false, !kVTrans);
 
@@ -283,8 +287,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             };
 
             // prologue: the first two half blocks of scores (both from K_0)
-            bool ok = mbar_wait(&bar_q_full[t], 0, abort_word, kDevTimeoutMma) &&
-                      mbar_wait(&bar_kv_full[kv_stage(0)], kv_phase(0), abort_word, kDevTimeoutMma);
+            bool ok = mbar_wait_warp(&bar_q_full[t], 0, abort_word, kDevTimeoutMma) &&
+                      mbar_wait_warp(&bar_kv_full[kv_stage(0)], kv_phase(0), abort_word, kDevTimeoutMma);
             if (ok) {
                 tc_fence_after_sync();
                 issue_s(0);
@@ -298,12 +302,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             // a P V product is read off the scores issued behind it.
             for (int g = 0; ok && g < n_halves; ++g) {
                 const bool more_s = g + 2 < n_halves;
-                if (!mbar_wait(&bar_p_full[t * 2 + (g & 1)], static_cast<uint32_t>((g >> 1) & 1), abort_word, kDevTimeoutMma)) break;
+                if (!mbar_wait_warp(&bar_p_full[t * 2 + (g & 1)], static_cast<uint32_t>((g >> 1) & 1), abort_word, kDevTimeoutMma)) break;
                 tc_fence_after_sync();
                 issue_pv(g);
                 if (more_s) issue_s(g + 2);   // commits to s_full
-                if (g == n_halves - 2) umma_commit(&bar_pv_done[t]);   // no scores follow this product
-                if (g == n_halves - 1) umma_commit(&bar_o_full[t]);
+                if (leader && g == n_halves - 2) umma_commit(&bar_pv_done[t]);   // no scores follow this product
+                if (leader && g == n_halves - 1) umma_commit(&bar_o_full[t]);
             }
         }
         __syncwarp();
