@@ -85,7 +85,8 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_acc_full + 1);
     volatile uint32_t* abort_word = tmem_slot + 1;
 
-    const int warp = threadIdx.x >> 5;
+    // broadcast from lane 0, so that the compiler knows the role of a warp to be the same for all its lanes
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
     const int lane = threadIdx.x & 31;
     const int j0 = blockIdx.x * HT;        // first hidden unit of this CTA
     const int b0 = blockIdx.y * kLstmBM;   // first batch row
@@ -112,11 +113,18 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0) {
-            tma_prefetch_desc(&tmap_x);
-            tma_prefetch_desc(&tmap_w);
-            tma_prefetch_desc(&tmap_h);
-            tma_prefetch_desc(&tmap_u);
+        // The producer and the MMA issuer run as whole warps with one elected lane executing the TMA, MMA and commit
+        // instructions: with every lane on the same path the address and descriptor arithmetic stays in the uniform
+        // datapath, whose registers those instructions read; behind a branch on the lane index every operand would be
+        // moved there first, a fixed cost per instruction that a step of this kernel pays some three hundred times.
+        const bool leader = elect_one_sync();
+        {
+            if (leader) {
+                tma_prefetch_desc(&tmap_x);
+                tma_prefetch_desc(&tmap_w);
+                tma_prefetch_desc(&tmap_h);
+                tma_prefetch_desc(&tmap_u);
+            }
             int stage = 0;
             uint32_t phase = 0;
             auto load_b = [&](int kbs, int slot, uint64_t* bar) {
@@ -135,9 +143,9 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             // which releases its own dependents early, is still running.
             grid_launch_dependents();
             for (int kb = 0; kb < k_blocks; kb += Cfg::kSub) {
-                if (!mbar_wait(&bar_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) break;
+                if (!mbar_wait_warp(&bar_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) break;
                 const int subs = min(Cfg::kSub, k_blocks - kb);
-                mbar_arrive_expect_tx(&bar_full[stage], static_cast<uint32_t>(subs * Cfg::kBlockBytes));
+                if (leader) mbar_arrive_expect_tx(&bar_full[stage], static_cast<uint32_t>(subs * Cfg::kBlockBytes));
                 for (int sub = 0; sub < subs; ++sub) {
                     // Every CTA of a batch tile reads the same x / h tiles: each starts at a different K block
                     // and wraps around, so that at any moment the CTAs pull different lines out of L2.
@@ -146,9 +154,11 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     const int part = from_x ? kb_x : kb_h;
                     const int kcoord = ((from_x ? kbs : kbs - kb_x) + static_cast<int>(blockIdx.x)) % part * kLstmBK;
                     const int slot = stage * Cfg::kSub + sub;
-                    tma_load_3d(smem_a + slot * Cfg::kABytes, from_x ? &tmap_x : &tmap_h, &bar_full[stage], kcoord, b0,
-                                from_x ? p.zx : p.zh);
-                    load_b(kbs, slot, &bar_full[stage]);
+                    if (leader) {
+                        tma_load_3d(smem_a + slot * Cfg::kABytes, from_x ? &tmap_x : &tmap_h, &bar_full[stage], kcoord, b0,
+                                    from_x ? p.zx : p.zh);
+                        load_b(kbs, slot, &bar_full[stage]);
+                    }
                 }
                 if (++stage == Cfg::kStages) {
                     stage = 0;
@@ -158,7 +168,8 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0) {
+        const bool leader = elect_one_sync();
+        {
             constexpr uint32_t idesc = make_idesc_f16_f32(kLstmBM, Cfg::kN, false, false);
             // The descriptors of a slot are those of slot 0 plus a constant: no address arithmetic between MMAs,
             // which the pipe would wait for (the issuing thread runs barely one MMA ahead of it).
@@ -168,7 +179,7 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             uint32_t phase = 0;
             bool ok = true;
             for (int kb = 0; kb < k_blocks; kb += Cfg::kSub) {
-                if (!mbar_wait(&bar_full[stage], phase, abort_word, kDevTimeoutMma)) {
+                if (!mbar_wait_warp(&bar_full[stage], phase, abort_word, kDevTimeoutMma)) {
                     ok = false;
                     break;
                 }
@@ -180,16 +191,17 @@ lstm_cell_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(slot * (Cfg::kBBytes >> 4));
 #pragma unroll
                     for (int k = 0; k < kLstmBK / 16; ++k)
-                        umma_f16_ss(tmem_base, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2),
-                                    idesc, (kb | sub | k) != 0);
+                        if (leader)
+                            umma_f16_ss(tmem_base, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2),
+                                        idesc, (kb | sub | k) != 0);
                 }
-                umma_commit(&bar_empty[stage]);
+                if (leader) umma_commit(&bar_empty[stage]);
                 if (++stage == Cfg::kStages) {
                     stage = 0;
                     phase ^= 1u;
                 }
             }
-            if (ok) umma_commit(bar_acc_full);
+            if (ok && leader) umma_commit(bar_acc_full);
         }
         __syncwarp();
     } else {
