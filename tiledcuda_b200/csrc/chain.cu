@@ -73,7 +73,8 @@ chain_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_o_full + 1);
     volatile uint32_t* abort_word = tmem_slot + 1;
 
-    const int warp = threadIdx.x >> 5;
+    // broadcast from lane 0, so that the compiler knows the role of a warp to be the same for all its lanes
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
     const int lane = threadIdx.x & 31;
     const int q0 = blockIdx.x * kChBM;
     const int bh = blockIdx.y;
@@ -116,59 +117,75 @@ chain_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            tma_prefetch_desc(&tmap_q);
-            tma_prefetch_desc(&tmap_k);
-            tma_prefetch_desc(&tmap_v);
+        // Producer and MMA issuer run as whole warps; one elected lane executes the TMA, MMA and commit instructions.
+        // With every lane on the same path the address and descriptor arithmetic stays in the uniform datapath, whose
+        // registers those instructions read; behind a branch on the lane index every operand is moved there first.
+        const bool leader = elect_one_sync();
+        {
+            if (leader) {
+                tma_prefetch_desc(&tmap_q);
+                tma_prefetch_desc(&tmap_k);
+                tma_prefetch_desc(&tmap_v);
+            }
             grid_dependency_wait();
-            mbar_arrive_expect_tx(bar_q_full, static_cast<uint32_t>(k_chunks * kChChunk));
-            for (int c = 0; c < k_chunks; ++c) tma_load_3d(s_q + c * kChChunk, &tmap_q, bar_q_full, c * 64, q0, bh);
+            if (leader) {
+                mbar_arrive_expect_tx(bar_q_full, static_cast<uint32_t>(k_chunks * kChChunk));
+                for (int c = 0; c < k_chunks; ++c) tma_load_3d(s_q + c * kChChunk, &tmap_q, bar_q_full, c * 64, q0, bh);
+            }
             const uint32_t v_bytes = kVTrans ? static_cast<uint32_t>(2 * p.dv * 128) : static_cast<uint32_t>(v_chunks * kChChunk);
             for (int j = 0; j < n_blocks; ++j) {
                 const int stage = j % kChStages;
                 const uint32_t phase = static_cast<uint32_t>((j / kChStages) & 1);
-                if (!mbar_wait(&bar_k_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) break;
-                mbar_arrive_expect_tx(&bar_k_full[stage], static_cast<uint32_t>(k_chunks * kChChunk));
-                for (int c = 0; c < k_chunks; ++c)
-                    tma_load_3d(s_k + stage * kChTile + c * kChChunk, &tmap_k, &bar_k_full[stage], c * 64, j * kChBN, bh);
-                if (!mbar_wait(&bar_v_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) break;
-                mbar_arrive_expect_tx(&bar_v_full[stage], v_bytes);
-                if (kVTrans) {
-                    // V^T rows are dv, inner dimension is kv: two 64-wide kv chunks of dv rows each
-                    for (int c = 0; c < 2; ++c)
-                        tma_load_3d(s_v + stage * kChTile + c * (p.dv * 128), &tmap_v, &bar_v_full[stage],
-                                    j * kChBN + c * 64, 0, bh);
-                } else {
-                    for (int c = 0; c < v_chunks; ++c)
-                        tma_load_3d(s_v + stage * kChTile + c * kChChunk, &tmap_v, &bar_v_full[stage], c * 64, j * kChBN, bh);
+                if (!mbar_wait_warp(&bar_k_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) break;
+                if (leader) {
+                    mbar_arrive_expect_tx(&bar_k_full[stage], static_cast<uint32_t>(k_chunks * kChChunk));
+                    for (int c = 0; c < k_chunks; ++c)
+                        tma_load_3d(s_k + stage * kChTile + c * kChChunk, &tmap_k, &bar_k_full[stage], c * 64, j * kChBN, bh);
+                }
+                if (!mbar_wait_warp(&bar_v_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) break;
+                if (leader) {
+                    mbar_arrive_expect_tx(&bar_v_full[stage], v_bytes);
+                    if (kVTrans) {
+                        // V^T rows are dv, inner dimension is kv: two 64-wide kv chunks of dv rows each
+                        for (int c = 0; c < 2; ++c)
+                            tma_load_3d(s_v + stage * kChTile + c * (p.dv * 128), &tmap_v, &bar_v_full[stage],
+                                        j * kChBN + c * 64, 0, bh);
+                    } else {
+                        for (int c = 0; c < v_chunks; ++c)
+                            tma_load_3d(s_v + stage * kChTile + c * kChChunk, &tmap_v, &bar_v_full[stage], c * 64, j * kChBN, bh);
+                    }
                 }
             }
         }
         __syncwarp();
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        const bool leader = elect_one_sync();
+        {
             const uint32_t idesc_s = make_idesc_f16_f32(kChBM, kChBN, false, false);
             const uint32_t idesc_o = make_idesc_f16_f32(kChBM, p.dv, false, !kVTrans);
-            bool ok = mbar_wait(bar_q_full, 0, abort_word, kDevTimeoutMma);
+            bool ok = mbar_wait_warp(bar_q_full, 0, abort_word, kDevTimeoutMma);
 
             auto issue_s = [&](int j) -> bool {
                 const int stage = j % kChStages;
                 const uint32_t phase = static_cast<uint32_t>((j / kChStages) & 1);
                 const int buf = j & 1;
                 const uint32_t buf_phase = static_cast<uint32_t>((j >> 1) & 1);
-                if (!mbar_wait(&bar_k_full[stage], phase, abort_word, kDevTimeoutMma)) return false;
-                if (!mbar_wait(&bar_s_empty[buf], buf_phase ^ 1u, abort_word, kDevTimeoutMma)) return false;
+                if (!mbar_wait_warp(&bar_k_full[stage], phase, abort_word, kDevTimeoutMma)) return false;
+                if (!mbar_wait_warp(&bar_s_empty[buf], buf_phase ^ 1u, abort_word, kDevTimeoutMma)) return false;
                 tc_fence_after_sync();
                 const uint32_t q_addr = smem_u32(s_q);
                 const uint32_t k_addr = smem_u32(s_k + stage * kChTile);
                 for (int kk = 0; kk < k_steps; ++kk) {
                     const uint32_t off = static_cast<uint32_t>((kk >> 2) * kChChunk + (kk & 3) * 32);
-                    umma_f16_ss(tmem_s0 + static_cast<uint32_t>(buf * kChBN), make_smem_desc_sw128(q_addr + off, 16, 1024),
-                                make_smem_desc_sw128(k_addr + off, 16, 1024), idesc_s, kk != 0);
+                    if (leader)
+                        umma_f16_ss(tmem_s0 + static_cast<uint32_t>(buf * kChBN), make_smem_desc_sw128(q_addr + off, 16, 1024),
+                                    make_smem_desc_sw128(k_addr + off, 16, 1024), idesc_s, kk != 0);
                 }
-                umma_commit(&bar_s_full[buf]);
-                umma_commit(&bar_k_empty[stage]);
+                if (leader) {
+                    umma_commit(&bar_s_full[buf]);
+                    umma_commit(&bar_k_empty[stage]);
+                }
                 return true;
             };
 
@@ -179,8 +196,8 @@ chain_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__
                 }
                 const int stage = j % kChStages;
                 const uint32_t phase = static_cast<uint32_t>((j / kChStages) & 1);
-                if (!mbar_wait(bar_p_full, static_cast<uint32_t>(j & 1), abort_word, kDevTimeoutMma)) break;
-                if (!mbar_wait(&bar_v_full[stage], phase, abort_word, kDevTimeoutMma)) break;
+                if (!mbar_wait_warp(bar_p_full, static_cast<uint32_t>(j & 1), abort_word, kDevTimeoutMma)) break;
+                if (!mbar_wait_warp(&bar_v_full[stage], phase, abort_word, kDevTimeoutMma)) break;
                 tc_fence_after_sync();
                 const uint32_t p_addr = smem_u32(s_p);
                 const uint32_t v_addr = smem_u32(s_v + stage * kChTile);
@@ -194,12 +211,14 @@ chain_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__
                         // MN-major: 16 kv rows of 128 bytes per step; dv chunks of 64 are kChChunk apart
                         b_desc = make_smem_desc_sw128(v_addr + static_cast<uint32_t>(kk * 2048), kChChunk, 1024);
                     }
-                    umma_f16_ss(tmem_o, make_smem_desc_sw128(p_addr + a_off, 16, 1024), b_desc, idesc_o, (j | kk) != 0);
+                    if (leader) umma_f16_ss(tmem_o, make_smem_desc_sw128(p_addr + a_off, 16, 1024), b_desc, idesc_o, (j | kk) != 0);
                 }
-                umma_commit(bar_p_empty);
-                umma_commit(&bar_v_empty[stage]);
+                if (leader) {
+                    umma_commit(bar_p_empty);
+                    umma_commit(&bar_v_empty[stage]);
+                }
             }
-            if (ok) umma_commit(bar_o_full);
+            if (ok && leader) umma_commit(bar_o_full);
         }
         __syncwarp();
     } else {

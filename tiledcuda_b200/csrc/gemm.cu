@@ -69,7 +69,8 @@ gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_acc_empty + 2);
     volatile uint32_t* abort_word = tmem_slot + 1;
 
-    const int warp = threadIdx.x >> 5;
+    // broadcast from lane 0, so that the compiler knows the role of a warp to be the same for all its lanes
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
     const int lane = threadIdx.x & 31;
     const int num_tiles = tiles_m * tiles_n;
     const int k_blocks = (K + kGemmBK - 1) / kGemmBK;
@@ -101,9 +102,15 @@ gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            tma_prefetch_desc(&tmap_a);
-            tma_prefetch_desc(&tmap_b);
+        // Producer and MMA issuer run as whole warps; one elected lane executes the TMA, MMA and commit instructions.
+        // With every lane on the same path the address and descriptor arithmetic stays in the uniform datapath, whose
+        // registers those instructions read; behind a branch on the lane index every operand is moved there first.
+        const bool leader = elect_one_sync();
+        {
+            if (leader) {
+                tma_prefetch_desc(&tmap_a);
+                tma_prefetch_desc(&tmap_b);
+            }
             grid_dependency_wait();
             int stage = 0;
             uint32_t phase = 0;
@@ -112,16 +119,18 @@ gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 int tm, tn;
                 gemm_tile_coords(tile, tiles_m, tiles_n, tm, tn);
                 for (int kb = 0; kb < k_blocks; kb += S::kSub) {
-                    if (!mbar_wait(&bar_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) {
+                    if (!mbar_wait_warp(&bar_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) {
                         ok = false;
                         break;
                     }
                     const int subs = min(S::kSub, k_blocks - kb);
-                    mbar_arrive_expect_tx(&bar_full[stage], static_cast<uint32_t>(subs * S::kStageBytes));
-                    for (int sub = 0; sub < subs; ++sub) {
-                        const int slot = stage * S::kSub + sub;
-                        tma_load_2d(smem_a + slot * S::kABytes, &tmap_a, &bar_full[stage], (kb + sub) * kGemmBK, tm * kGemmBM);
-                        tma_load_2d(smem_b + slot * S::kBBytes, &tmap_b, &bar_full[stage], (kb + sub) * kGemmBK, tn * BN);
+                    if (leader) {
+                        mbar_arrive_expect_tx(&bar_full[stage], static_cast<uint32_t>(subs * S::kStageBytes));
+                        for (int sub = 0; sub < subs; ++sub) {
+                            const int slot = stage * S::kSub + sub;
+                            tma_load_2d(smem_a + slot * S::kABytes, &tmap_a, &bar_full[stage], (kb + sub) * kGemmBK, tm * kGemmBM);
+                            tma_load_2d(smem_b + slot * S::kBBytes, &tmap_b, &bar_full[stage], (kb + sub) * kGemmBK, tn * BN);
+                        }
                     }
                     if (++stage == S::kRing) {
                         stage = 0;
@@ -133,7 +142,8 @@ gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         __syncwarp();
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        const bool leader = elect_one_sync();
+        {
             const uint32_t idesc = make_idesc_f16_f32(kGemmBM, BN, false, false) | idesc_extra;
             const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem_a), 16, 1024);
             const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem_b), 16, 1024);
@@ -143,11 +153,11 @@ gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint32_t acc_phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-                if (!mbar_wait(&bar_acc_empty[acc], acc_phase ^ 1u, abort_word, kDevTimeoutMma)) break;
+                if (!mbar_wait_warp(&bar_acc_empty[acc], acc_phase ^ 1u, abort_word, kDevTimeoutMma)) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
                 for (int kb = 0; kb < k_blocks; kb += S::kSub) {
-                    if (!mbar_wait(&bar_full[stage], phase, abort_word, kDevTimeoutMma)) {
+                    if (!mbar_wait_warp(&bar_full[stage], phase, abort_word, kDevTimeoutMma)) {
                         ok = false;
                         break;
                     }
@@ -161,18 +171,19 @@ gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
                         for (int k = 0; k < kGemmBK / 16; ++k) {
                             // +32 bytes per K=16 step inside the 128-byte swizzle row
-                            umma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2),
-                                        idesc, (kb | sub | k) != 0);
+                            if (leader)
+                                umma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2),
+                                            idesc, (kb | sub | k) != 0);
                         }
                     }
-                    umma_commit(&bar_empty[stage]);
+                    if (leader) umma_commit(&bar_empty[stage]);
                     if (++stage == S::kRing) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (!ok) break;
-                umma_commit(&bar_acc_full[acc]);
+                if (leader) umma_commit(&bar_acc_full[acc]);
                 if (++acc == 2) {
                     acc = 0;
                     acc_phase ^= 1u;

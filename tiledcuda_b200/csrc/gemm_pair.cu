@@ -61,9 +61,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_acc_empty + 2);
     volatile uint32_t* abort_word = tmem_slot + 1;
 
-    const int warp = threadIdx.x >> 5;
+    // both broadcast from lane 0, so that the compiler knows a warp's role to be the same for all its lanes
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
     const int lane = threadIdx.x & 31;
-    const uint32_t rank = cluster_ctarank();   // 0 = leader
+    const uint32_t rank = __shfl_sync(0xffffffffu, cluster_ctarank(), 0);   // 0 = leader
     const int pair = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
     const int num_tiles = tiles_m * tiles_n;
@@ -95,9 +96,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
-        if (lane == 0) {
-            tma_prefetch_desc(&tmap_a);
-            tma_prefetch_desc(&tmap_b);
+        // The producer runs as a whole warp and one elected lane executes the TMA instructions: with every lane on the
+        // same path the address arithmetic stays in the uniform datapath, whose registers those instructions read.
+        // The MMA issuer below stays a single lane: its MMAs are long enough (128 cycles each) to hide the operand
+        // moves, and the warp-wide form measured slower here (4096^3: 124 against 104 us).
+        const bool leader = elect_one_sync();
+        {
+            if (leader) {
+                tma_prefetch_desc(&tmap_a);
+                tma_prefetch_desc(&tmap_b);
+            }
             grid_dependency_wait();
             int stage = 0;
             uint32_t phase = 0;
@@ -108,17 +116,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const int row_a = tm * (2 * kPairBM) + static_cast<int>(rank) * kPairBM;
                 const int row_b = tn * kPairBN + static_cast<int>(rank) * (kPairBN / 2);
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait(&bar_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) {
+                    if (!mbar_wait_warp(&bar_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) {
                         ok = false;
                         break;
                     }
                     // the leader's full barrier counts the bytes of both CTAs
                     const uint32_t full_addr = map_to_cta(smem_u32(&bar_full[stage]), 0);
-                    if (rank == 0) mbar_arrive_expect_tx(&bar_full[stage], 2 * kPairStageBytes);
+                    if (leader) {
+                        if (rank == 0) mbar_arrive_expect_tx(&bar_full[stage], 2 * kPairStageBytes);
 #pragma unroll
-                    for (int c = 0; c < kPairBK / 64; ++c) {
-                        tma_load_2d_pair(smem_a + stage * kPairABytes + c * (kPairBM * 128), &tmap_a, full_addr, kb * kPairBK + c * 64, row_a);
-                        tma_load_2d_pair(smem_b + stage * kPairBBytes + c * ((kPairBN / 2) * 128), &tmap_b, full_addr, kb * kPairBK + c * 64, row_b);
+                        for (int c = 0; c < kPairBK / 64; ++c) {
+                            tma_load_2d_pair(smem_a + stage * kPairABytes + c * (kPairBM * 128), &tmap_a, full_addr, kb * kPairBK + c * 64, row_a);
+                            tma_load_2d_pair(smem_b + stage * kPairBBytes + c * ((kPairBN / 2) * 128), &tmap_b, full_addr, kb * kPairBK + c * 64, row_b);
+                        }
                     }
                     if (++stage == kPairStages) {
                         stage = 0;
@@ -257,9 +267,10 @@ gemm_pair_tall_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_acc_empty + 2);
     volatile uint32_t* abort_word = tmem_slot + 1;
 
-    const int warp = threadIdx.x >> 5;
+    // both broadcast from lane 0, so that the compiler knows a warp's role to be the same for all its lanes
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
     const int lane = threadIdx.x & 31;
-    const uint32_t rank = cluster_ctarank();   // 0 = leader
+    const uint32_t rank = __shfl_sync(0xffffffffu, cluster_ctarank(), 0);   // 0 = leader
     const int pair = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
     const int num_tiles = tiles_m * tiles_n;
@@ -291,9 +302,16 @@ gemm_pair_tall_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
-        if (lane == 0) {
-            tma_prefetch_desc(&tmap_a);
-            tma_prefetch_desc(&tmap_b);
+        // The producer runs as a whole warp and one elected lane executes the TMA instructions: with every lane on the
+        // same path the address arithmetic stays in the uniform datapath, whose registers those instructions read.
+        // The MMA issuer below stays a single lane: its MMAs are long enough (128 cycles each) to hide the operand
+        // moves, and the warp-wide form measured slower here (4096^3: 124 against 104 us).
+        const bool leader = elect_one_sync();
+        {
+            if (leader) {
+                tma_prefetch_desc(&tmap_a);
+                tma_prefetch_desc(&tmap_b);
+            }
             grid_dependency_wait();
             int stage = 0;
             uint32_t phase = 0;
@@ -304,16 +322,18 @@ gemm_pair_tall_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 const int row_a = tm * (4 * kPairBM) + static_cast<int>(rank) * (2 * kPairBM);
                 const int row_b = tn * kPairBN + static_cast<int>(rank) * (kPairBN / 2);
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait(&bar_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) {
+                    if (!mbar_wait_warp(&bar_empty[stage], phase ^ 1u, abort_word, kDevTimeoutProducer)) {
                         ok = false;
                         break;
                     }
                     const uint32_t full_addr = map_to_cta(smem_u32(&bar_full[stage]), 0);
-                    if (rank == 0) mbar_arrive_expect_tx(&bar_full[stage], 2 * kTallStageBytes);
                     uint8_t* a_dst = smem_a + stage * kTallABytes;
-                    tma_load_2d_pair(a_dst, &tmap_a, full_addr, kb * kTallBK, row_a);
-                    tma_load_2d_pair(smem_b + stage * kTallBBytes, &tmap_b, full_addr, kb * kTallBK, row_b);
-                    tma_load_2d_pair(a_dst + kPairBM * 128, &tmap_a, full_addr, kb * kTallBK, row_a + kPairBM);
+                    if (leader) {
+                        if (rank == 0) mbar_arrive_expect_tx(&bar_full[stage], 2 * kTallStageBytes);
+                        tma_load_2d_pair(a_dst, &tmap_a, full_addr, kb * kTallBK, row_a);
+                        tma_load_2d_pair(smem_b + stage * kTallBBytes, &tmap_b, full_addr, kb * kTallBK, row_b);
+                        tma_load_2d_pair(a_dst + kPairBM * 128, &tmap_a, full_addr, kb * kTallBK, row_a + kPairBM);
+                    }
                     if (++stage == kTallStages) {
                         stage = 0;
                         phase ^= 1u;
