@@ -7,12 +7,17 @@
 //                rows; each tile owns two 64-column score buffers in TMEM. For half block g the issuer of tile t issues
 //                O_t += P_t(g) V(g) (A operand read from TMEM) and then S_t(g+2) = Q_t K(g+2)^T into the
 //                buffer P_t(g) just vacated, so the scores of the next half block are ready while the
-//                softmax warps still work on the current one;
+//                softmax warps still work on the current one. The whole warp runs the loop, one elected lane
+//                executes the MMAs; the loop holds one barrier wait and one commit per half block;
+//   warp 3       forwarder: adds "the K / V tiles this step needs have landed" to the barrier the issuers wait on
+//                anyway (P of half block g written), so that the issuers wait for nothing else;
 //   warps 4..7   softmax warpgroup of tile 0, warps 8..11 of tile 1: one thread per query row. tcgen05.ld
 //                64 fp32 scores, online softmax with fp32 running maximum and sum (exp2, scale folded
 //                in), round to fp16 and tcgen05.st P over the columns the scores came from: P never
 //                leaves TMEM. O_t stays in TMEM, is rescaled only when the row maximum grew by more
 //                than 2^8 (after waiting for the PV product in flight), and is normalised once at the end.
+//                These warps also hand the ring stages back to the producer: the MMAs of a CTA complete in
+//                issue order, so seeing the scores of half block g means every older MMA has read its operands.
 // TMEM: S_0a S_0b | S_1a S_1b | O_0 | O_1 (64, 64, 64, 64, 128, 128 columns). tcgen05.mma instructions
 // of one CTA execute in issue order, so S_t(g+2) may overwrite P_t(g) right after P_t(g) V(g) was issued.
 //
