@@ -466,18 +466,49 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-// 2^x on the FMA pipe, for x <= ~100: floor(x) by the round-down magic-number add, a degree-3 minimax
+// ---- packed fp32 pairs: one instruction does the arithmetic of two values (sm_100: add / mul / fma .f32x2) ----
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2_round_down(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rm.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
+// 2^x of two values on the FMA pipe, for x <= ~100: floor(x) by the round-down magic-number add, a degree-3 minimax
 // polynomial for 2^frac on [0, 1) (max relative error 7.5e-5, below fp16 resolution), and the integer part
-// added into the exponent field. Takes load off the 16-lane special-function unit, which exponentials of an
-// attention tile otherwise saturate.
-__device__ __forceinline__ float poly_exp2(float x) {
-    x = fmaxf(x, -126.f);
-    float y;
-    asm("add.rm.f32 %0, %1, %2;" : "=f"(y) : "f"(x), "f"(12582912.f));   // 1.5 * 2^23: the low mantissa bits now hold floor(x)
-    const float fl = y - 12582912.f;
-    const float f = x - fl;
-    const float p = fmaf(fmaf(fmaf(0.07802422344684601f, f, 0.22606723010540009f), f, 0.695833683013916f), f, 0.9999251961708069f);
-    return __int_as_float(__float_as_int(p) + (__float_as_int(y) << 23));
+// added into the exponent field. Takes load off the 16-lane special-function unit, which the exponentials of an
+// attention tile otherwise saturate. xa and xb are the two halves of x2 (the caller has them unpacked anyway).
+__device__ __forceinline__ void poly_exp2_pair(float xa, float xb, float& a, float& b) {
+    const uint64_t magic = pack2(12582912.f, 12582912.f);   // 1.5 * 2^23: the low mantissa bits of the sum hold floor(x)
+    const uint64_t xc = pack2(fmaxf(xa, -126.f), fmaxf(xb, -126.f));
+    const uint64_t y = add2_round_down(xc, magic);
+    const uint64_t fl = add2(y, pack2(-12582912.f, -12582912.f));
+    const uint64_t f = fma2(fl, pack2(-1.f, -1.f), xc);
+    uint64_t q = fma2(pack2(0.07802422344684601f, 0.07802422344684601f), f, pack2(0.22606723010540009f, 0.22606723010540009f));
+    q = fma2(q, f, pack2(0.695833683013916f, 0.695833683013916f));
+    q = fma2(q, f, pack2(0.9999251961708069f, 0.9999251961708069f));
+    float qa, qb, ya, yb;
+    unpack2(q, qa, qb);
+    unpack2(y, ya, yb);
+    a = __int_as_float(__float_as_int(qa) + (__float_as_int(ya) << 23));
+    b = __int_as_float(__float_as_int(qb) + (__float_as_int(yb) << 23));
 }
 
 // max of three (one instruction on sm_100)
