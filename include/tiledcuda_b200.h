@@ -99,7 +99,7 @@ int tc_b2b_gemm_f16(const void* A, const void* B, const void* D, void* E, int64_
  * [batch,heads,head_dim_v,seq_kv] (the layout the reference's Python wrapper produces) otherwise.
  * lse (fp32 [batch,heads,seq_q], natural log of the softmax denominator) may be NULL.
  * Softmax statistics are fp32. Needs head_dim, head_dim_v multiples of 16 and <= 128; seq_kv % 8 == 0 when V is
- * transposed (rows of V^T are 16-byte granular); scale finite, and non-zero when seq_q > 128 and seq_kv % 64 != 0.
+ * transposed (rows of V^T are 16-byte granular); scale finite (zero weighs every KV row the same).
  * Replaces `flash_attention` / `run_flash_attention` / `custom_flash_attention_op`
  * (src/kernels/flash_attn.cu:134-312, 314-422, 424-456); the reference fixes scale = 1. */
 int tc_flash_attn_fwd_f16(const void* Q, const void* K, const void* V, void* O, float* lse, int64_t batch,
@@ -110,7 +110,7 @@ int tc_flash_attn_fwd_f16(const void* Q, const void* K, const void* V, void* O, 
  * reference: its flash_attention, src/kernels/flash_attn.cu:134-312, is non-causal over
  * [batch*heads, seq, dim] operands). causal != 0: query row i sees KV rows j <= i + (seq_kv - seq_q),
  * i.e. the mask is aligned to the bottom-right corner; KV blocks above the diagonal are skipped, a row
- * that sees no KV row yields zeros and lse = -inf; scale must be non-zero. seq_major != 0: Q, K, V and O
+ * that sees no KV row yields zeros and lse = -inf. seq_major != 0: Q, K, V and O
  * are [batch, seq, heads, dim] (heads interleaved per token, as a fused QKV projection leaves them)
  * instead of [batch, heads, seq, dim]; not together with a transposed V. lse stays [batch, heads, seq_q]. */
 int tc_flash_attn_fwd_ex_f16(const void* Q, const void* K, const void* V, void* O, float* lse, int64_t batch,

@@ -62,7 +62,6 @@ def test_every_declaration_cites_the_reference_or_says_it_has_no_counterpart():
         (lambda l: l.tc_lstm_cell_f16(16, 16, None, 16, 32, 16, 32, 16, 8, 64, 32, None), "alias"),
         (lambda l: l.tc_lstm_chain_f16(16, 16, None, 16, 16, 16, 16, 16, 0, 8, 64, 32, None), "steps"),
         (lambda l: l.tc_lstm_chain_static_f16(16, 16, None, 16, 16, 16, 16, 16, -1, 8, 64, 32, None), "negative"),
-        (lambda l: l.tc_flash_attn_fwd_f16(16, 16, 16, 16, None, 1, 1, 256, 104, 64, 64, 0.0, 0, None), "scale == 0"),
     ],
 )
 def test_bad_arguments_return_a_status_and_a_message(call, needle):

@@ -339,8 +339,26 @@ def test_flash_attn_ex_rejects_bad_combinations(cuda_ops, clean_status):
     q = torch.zeros(1, 64, 2, 64, dtype=torch.float16, device=DEV)
     with pytest.raises(ValueError):
         cuda_ops.flash_attn(q, q, q, torch.empty_like(q), seq_major=True, v_is_transposed=True)
-    with pytest.raises(RuntimeError, match="non-zero scale"):
-        cuda_ops.flash_attn(q, q, q, torch.empty_like(q), causal=True, scale=0.0)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("sq,skv", [(256, 104), (384, 200), (128, 72)])
+def test_flash_attn_with_a_zero_scale_averages_the_visible_rows(cuda_ops, clean_status, causal, sq, skv):
+    """scale == 0 gives every visible KV row the same weight, also where columns are masked (a ragged last half block,
+    the causal diagonal): masking is applied after scaling."""
+    torch.manual_seed(5)
+    q = torch.randn(1, 2, sq, 64, device=DEV).half()
+    k = torch.randn(1, 2, skv, 64, device=DEV).half()
+    v = torch.randn(1, 2, skv, 64, device=DEV).half()
+    o = torch.full((1, 2, sq, 64), float("nan"), dtype=torch.float16, device=DEV)
+    cuda_ops.flash_attn(q, k, v, o, causal=causal, scale=0.0)
+    vf = v.float().cpu()
+    want = torch.zeros(1, 2, sq, 64)
+    for i in range(sq):
+        visible = min(skv, i + (skv - sq) + 1) if causal else skv
+        if visible > 0:
+            want[:, :, i] = vf[:, :, :visible].mean(dim=2)
+    assert torch.allclose(o.float().cpu(), want, atol=2e-3, rtol=2e-3)
 
 
 def test_flash_attn_large_scores_need_rescaling(cuda_ops, clean_status):

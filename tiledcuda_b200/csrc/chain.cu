@@ -474,13 +474,10 @@ static int attn_entry(const char* op, const void* Q, const void* K, const void* 
     TCB_REQUIRE(head_dim % 8 == 0 && head_dim_v % 8 == 0, "%s: head dims must be multiples of 8", op);
     TCB_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(V) && aligned16(O), "%s: pointers must be 16-byte aligned", op);
     TCB_REQUIRE(isfinite(scale), "%s: scale is not finite", op);
-    TCB_REQUIRE(!causal || scale != 0.f, "%s: a causal mask needs a non-zero scale", op);
     auto* st = static_cast<cudaStream_t>(stream);
     const bool two_tiles = seq_q > kChBM || causal || seq_major;
-    // The two-tile kernel masks a score by setting it to the infinity whose product with the scale is -inf, which
-    // has no meaning for scale == 0; it masks whenever the last 64 KV rows are not all there.
-    TCB_REQUIRE(!(two_tiles && scale == 0.f && seq_kv % 64 != 0),
-                "%s: scale == 0 needs seq_kv to be a multiple of 64 for this shape (got %lld)", op, (long long)seq_kv);
+    // Both kernels mask after scaling (a masked column is -inf whatever the scale), so scale == 0, which makes every
+    // visible KV row weigh the same, needs no special case.
     if (two_tiles)
         return launch_attn_pingpong(Q, K, V, O, lse, batch, heads, seq_q, seq_kv, head_dim, head_dim_v, scale,
                                     v_is_transposed != 0, causal != 0, seq_major != 0, st);
