@@ -60,7 +60,7 @@ SUSTAINED_SECONDS = 2.0
 NCU_TRAFFIC_BYTES: dict[str, int | None] = {
     "gemm8192": 1_079_000_000,   # profiles/gemm_8192_ncu.md
     "scatter": 1_387_700_000,    # profiles/scatter_nd_c5_ncu.md
-    "fa": 2_128_600_000,         # profiles/flash_attn_c3_ncu.md
+    "fa": 2_130_000_000,         # profiles/flash_attn_c3_ncu.md
     "b2b": 12_680_000,           # profiles/b2b_gemm_c2_ncu.md (4.29 MB read in the kernel + 8.39 MB result written back)
 }
 
