@@ -471,7 +471,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             for (int c = 0; c < v_chunks; ++c)
                 tma_store_4d(&tmap_o, s_q + t * kFaTile + c * kFaChunk, c * 64, q0 + t * kFaBM, head, bat);
             tma_store_commit();
-            tma_store_wait<0>();   // the tile has left shared memory and reached the output before the CTA may exit
+            tma_store_wait_read<0>();   // the tile has left shared memory; the grid's completion covers the writes
         }
     }
 

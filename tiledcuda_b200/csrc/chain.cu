@@ -357,7 +357,7 @@ chain_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__
                     }
                     sbuf ^= 1;
                 }
-                if (lane == 0) tma_store_wait<0>();
+                if (lane == 0) tma_store_wait_read<0>();
             } else {
 #pragma unroll 1
                 for (int c = 0; c < p.dv / 16; ++c) {

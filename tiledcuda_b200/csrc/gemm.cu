@@ -216,7 +216,7 @@ gemm_f16_f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 acc_phase ^= 1u;
             }
         }
-        if (use_tma && lane == 0) tma_store_wait<0>();   // all boxes written before the CTA may exit
+        if (use_tma && lane == 0) tma_store_wait_read<0>();   // shared memory has been read; the grid's completion covers the writes
     }
 
     // ---------------- teardown ----------------

@@ -221,7 +221,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 acc_phase ^= 1u;
             }
         }
-        if (use_tma && lane == 0) tma_store_wait<0>();   // all boxes written before the CTA may exit
+        if (use_tma && lane == 0) tma_store_wait_read<0>();   // shared memory has been read; the grid's completion covers the writes
     }
 
     // ---------------- teardown: neither CTA frees TMEM or exits while its peer may still touch it ----------------
@@ -441,7 +441,7 @@ gemm_pair_tall_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             }
             tile_phase ^= 1u;
         }
-        if (use_tma && lane == 0) tma_store_wait<0>();
+        if (use_tma && lane == 0) tma_store_wait_read<0>();
     }
 
     // ---------------- teardown ----------------
