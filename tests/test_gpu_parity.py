@@ -252,6 +252,8 @@ def test_flash_attention_fwd_reference_signature_and_golden(cuda_ops, clean_stat
         (2, 3, 256, 384, 64, 64, False), (1, 2, 200, 328, 128, 128, False), (1, 2, 200, 328, 128, 128, True),
         (1, 1, 1, 8, 16, 16, False), (1, 2, 77, 1001, 80, 48, False), (1, 1, 130, 72, 32, 128, True),
         (2, 4, 1024, 1024, 128, 128, False),
+        # more than one query tile against one, two and three half blocks of KV rows (the shortest pipelines of the two-tile kernel)
+        (1, 2, 256, 64, 64, 64, False), (1, 1, 300, 40, 128, 128, False), (1, 2, 384, 128, 128, 128, False), (1, 1, 512, 192, 128, 128, False),
     ],
 )
 def test_flash_attn_matches_oracle(cuda_ops, clean_status, b, h, sq, skv, d, dv, vt):
