@@ -447,8 +447,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             const float inv_l = l_sum > 0.f ? 1.f / l_sum : 0.f;   // a fully masked row yields zeros
             const int r_in_tile = quarter * 32 + lane;
             uint8_t* stage_row = s_q + t * kFaTile + r_in_tile * 128;
+            int c = 0;
 #pragma unroll 1
-            for (int c = 0; c < p.dv / 16; ++c) {
+            // 64 columns per round trip to TMEM while they last (each trip costs its latency once), 16 for the rest
+            for (; c + 4 <= p.dv / 16; c += 4) {
+                uint32_t r[64];
+                tmem_ld_x32(o_addr + static_cast<uint32_t>(c * 16), *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+                tmem_ld_x32(o_addr + static_cast<uint32_t>(c * 16 + 32), *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+                tmem_ld_wait();
+                uint8_t* chunk = stage_row + (c >> 2) * kFaChunk;
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    uint32_t h[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        h[i] = pack_half2(__uint_as_float(r[cc * 16 + 2 * i]) * inv_l, __uint_as_float(r[cc * 16 + 2 * i + 1]) * inv_l);
+                    const int piece = cc * 2;
+                    *reinterpret_cast<uint4*>(chunk + (((piece) ^ (r_in_tile & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+                    *reinterpret_cast<uint4*>(chunk + (((piece + 1) ^ (r_in_tile & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+                }
+            }
+#pragma unroll 1
+            for (; c < p.dv / 16; ++c) {
                 uint32_t r[16];
                 tmem_ld_x16(o_addr + static_cast<uint32_t>(c * 16), r);
                 tmem_ld_wait();
