@@ -262,7 +262,9 @@ class OverlappedAssembly:
 
     def __init__(self, blocks: int = 4, copy_streams: int = 1):
         # one copy stream: with the (rank + s) schedule every GPU then receives from one sender at a time, which
-        # measured fastest on eight GPUs (2.00 ms for the 16384^3 GEMM against 2.22 / 2.88 ms with 7 / 4 streams)
+        # measured fastest on eight GPUs (2.00 ms for the 16384^3 GEMM against 2.22 / 2.88 ms with 7 / 4 streams).
+        # Every peer copy costs about 34 us on top of its bytes, so on eight GPUs fewer blocks win (two: 1.89 ms,
+        # four: 2.00, eight: 2.33), while on two or four, where the step is compute-bound, four or eight do.
         self.blocks = max(1, blocks)
         self.copy_streams = max(1, copy_streams)
         self.windows = None
